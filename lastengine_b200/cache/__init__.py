@@ -1,2 +1,2 @@
 from .allocator import CacheError, CacheFull, IdPool  # noqa: F401
-from .cache import PAGE_SIZE, Cache, CacheView  # noqa: F401
+from .cache import PAGE_SIZE, Cache, CacheView, pooled_table_key  # noqa: F401

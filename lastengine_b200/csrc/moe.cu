@@ -16,14 +16,68 @@
 // The softmax router (mode ROUTER_SOFTMAX_CHOSEN in the place of norm_topk): logits z + bias, the bias
 // part of the logit; the k largest are chosen and weighted by the softmax over the chosen logits alone.
 #define ROUTER_SOFTMAX_CHOSEN 2
+// The grouped softmax router (mode ROUTER_SOFTMAX_GROUPED, with the number of groups and of kept groups in the
+// bits above the mode): scores s = softmax(z) over all experts; choice scores c = s + bias (the bias chooses, it
+// does not weigh); the experts form `groups` equal groups of neighbours, a group's score is its largest c, and
+// only experts of the `keep` best groups (ties to the lower group) can be chosen: the others' c counts as minus
+// infinity.  Weights: the chosen s over their sum (+ 1e-20).
+#define ROUTER_SOFTMAX_GROUPED 3
+#define ROUTER_MODE(m) ((m) & 255)
+#define ROUTER_GROUPS(m) (((m) >> 8) & 255)
+#define ROUTER_KEEP(m) (((m) >> 16) & 255)
 __device__ __forceinline__ void router_score(float* s, float* c, float z, float b, int mode) {
-  if (mode == ROUTER_SOFTMAX_CHOSEN) {
+  if (ROUTER_MODE(mode) == ROUTER_SOFTMAX_GROUPED) {
+    *s = *c = z;       // the logit for now: router_softmax_groups turns a row's logits into s and c
+  } else if (mode == ROUTER_SOFTMAX_CHOSEN) {
     *s = *c = z + b;
   } else {
     const float sg = 1.0f / (1.0f + expf(-z));
     *s = sg;
     *c = sg + b;
   }
+}
+
+// One row of the grouped softmax router by one warp, between the logits and the choice.
+__device__ __forceinline__ void router_softmax_groups(float* __restrict__ s, float* __restrict__ c,
+                                                      const float* __restrict__ bias, int E, int groups, int keep, int lane) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(s[e] - mx);
+  sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(s[e] - mx) / sum;
+    s[e] = p;
+    c[e] = p + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    // every lane finds the kept groups for itself (a few dozen comparisons): group scores, then `keep` picks
+    unsigned long long kept_lo = 0, kept_hi = 0, kept_2 = 0, kept_3 = 0;   // up to 256 groups
+    for (int j = 0; j < keep; j++) {
+      float bv = -INFINITY;
+      int bg = -1;
+      for (int g = 0; g < groups; g++) {
+        const unsigned long long bit = 1ull << (g & 63);
+        const unsigned long long word = g < 64 ? kept_lo : (g < 128 ? kept_hi : (g < 192 ? kept_2 : kept_3));
+        if (word & bit) continue;
+        float gs = -INFINITY;
+        for (int q = 0; q < per; q++) gs = fmaxf(gs, c[g * per + q]);
+        if (bg < 0 || gs > bv) { bv = gs; bg = g; }
+      }
+      const unsigned long long bit = 1ull << (bg & 63);
+      if (bg < 64) kept_lo |= bit; else if (bg < 128) kept_hi |= bit; else if (bg < 192) kept_2 |= bit; else kept_3 |= bit;
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+      const int g = e / per;
+      const unsigned long long word = g < 64 ? kept_lo : (g < 128 ? kept_hi : (g < 192 ? kept_2 : kept_3));
+      if (!(word & (1ull << (g & 63)))) c[e] = -INFINITY;
+    }
+  }
+  __syncwarp();
 }
 
 // One row's choice by one warp: the k largest selection scores c, ties to the lower index; the
@@ -54,7 +108,8 @@ __device__ __forceinline__ void router_choose(int* __restrict__ ids, float* __re
   if (lane == 0) {
     for (int j = 0; j < k; j++) {
       float w = norm_topk == ROUTER_SOFTMAX_CHOSEN ? expf(sg[chosen[j]] - sg[chosen[0]]) : sg[chosen[j]];
-      if (norm_topk) w = w / sum;
+      if (ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED) w = w / (sum + 1e-20f);
+      else if (norm_topk) w = w / sum;
       ids[j] = chosen[j];
       wts[j] = w * scaling;
     }
@@ -130,6 +185,8 @@ moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, const 
   // the k largest c of each row, ties to the lower index: warp r' takes rows r', r' + warps, ...
   for (int r = warp; r < R; r += nw) {
     if (m0 + r >= M) continue;
+    if (ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED)
+      router_softmax_groups(s_ + r * E, c_ + r * E, bias, E, ROUTER_GROUPS(norm_topk), ROUTER_KEEP(norm_topk), lane);
     router_choose(topk_ids + (size_t)(m0 + r) * k, topk_w + (size_t)(m0 + r) * k, c_ + r * E, s_ + r * E, E, k, norm_topk,
                   scaling, lane);
   }
@@ -222,6 +279,8 @@ moe_router_rows_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, c
   __syncthreads();
   for (int r = warp; r < RB; r += 8) {
     if (m0 + r >= M) continue;
+    if (ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED)
+      router_softmax_groups(s_ + r * E, c_ + r * E, bias, E, ROUTER_GROUPS(norm_topk), ROUTER_KEEP(norm_topk), lane);
     router_choose(topk_ids + (size_t)(m0 + r) * k, topk_w + (size_t)(m0 + r) * k, c_ + r * E, s_ + r * E, E, k, norm_topk,
                   scaling, lane);
   }

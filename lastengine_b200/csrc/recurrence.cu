@@ -1,0 +1,414 @@
+// Linear recurrences with a matrix state per head, for packed rows of several sequences, and the
+// small kernels around them.  Everything here is float: the design rule of the mixers that use it is
+// that whatever enters a recurrence (decays, step sizes, write strengths, unit norms, the state) is 32-bit.
+//
+// The recurrence (leb_gated_recurrence), per head h with state S [d, e] and, per row t, a key k_t [d],
+// a query q_t [d], a value v_t [e], a write strength w_t and a decay a_t (a number per head, or one per
+// key channel):
+//     S <- diag(a_t) S
+//     u  = w_t v_t                    plain form (state-space layers: k = B, q = C, w = dt)
+//     u  = w_t (v_t - S^T k_t)        delta form (the write replaces what the key already reads)
+//     S <- S + k_t u^T
+//     o_t = S^T q_t (+ skip_h v_t)
+// in this order: the read-out sees the row's own write.  Several heads may share one key/query head
+// (head h reads key head h / (H / Gk)).
+//
+// The columns of S never mix, so a warp owns one column (lane r holds rows r, r + 32, ...) and walks
+// the sequence's rows of the step in order; k, q, a, v and w of the next row are fetched while the
+// current one is computed.  The state is kept [slot][head][column][row] so that a warp's column is
+// one contiguous run.  The same kernel serves prompts, portions and decode steps: a row's result
+// depends only on the state before it and the rows of its own sequence.
+#include "common.cuh"
+
+constexpr int REC_WARPS = 8;      // columns per block
+
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+template <int RL, bool DELTA, bool ROW_DECAY>
+__global__ void __launch_bounds__(32 * REC_WARPS)
+gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restrict__ k, const float* __restrict__ q, int ldk,
+                        const float* __restrict__ v, int ldv, const float* __restrict__ wr, int ldw,
+                        const float* __restrict__ decay, int ldd, const float* __restrict__ skip,
+                        float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                        const int* __restrict__ seq_qlen, int H, int Gk, int d, int e) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * REC_WARPS + warp;
+  if (c >= e) return;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int slot = seq_slot[b];
+  const int n = seq_qlen ? seq_qlen[b] : 1;
+  const int m0 = seq_qstart[b];
+  const int kh = h / (H / Gk);
+  float* sp = slot >= 0 ? state + (((size_t)slot * H + h) * e + c) * d : nullptr;
+  float s[RL];
+#pragma unroll
+  for (int i = 0; i < RL; i++) {
+    const int r = lane + 32 * i;
+    s[i] = (sp && r < d) ? sp[r] : 0.f;
+  }
+  const float sk = skip ? skip[h] : 0.f;
+  // the first row's operands
+  float kc[RL], qc[RL], ac[RL], vc, wc;
+  {
+    const size_t m = m0;
+#pragma unroll
+    for (int i = 0; i < RL; i++) {
+      const int r = lane + 32 * i;
+      const bool in = r < d && n > 0;
+      kc[i] = in ? k[m * ldk + kh * d + r] : 0.f;
+      qc[i] = in ? q[m * ldk + kh * d + r] : 0.f;
+      ac[i] = in ? (ROW_DECAY ? decay[m * ldd + h * d + r] : decay[m * ldd + h]) : 0.f;
+    }
+    vc = n > 0 ? v[m * ldv + h * e + c] : 0.f;
+    wc = n > 0 ? wr[m * ldw + h] : 0.f;
+  }
+  for (int t = 0; t < n; t++) {
+    const size_t m = (size_t)m0 + t;
+    float kn[RL], qn[RL], an[RL], vn = 0.f, wn = 0.f;
+    const bool more = t + 1 < n;
+#pragma unroll
+    for (int i = 0; i < RL; i++) {
+      const int r = lane + 32 * i;
+      const bool in = more && r < d;
+      kn[i] = in ? k[(m + 1) * ldk + kh * d + r] : 0.f;
+      qn[i] = in ? q[(m + 1) * ldk + kh * d + r] : 0.f;
+      an[i] = in ? (ROW_DECAY ? decay[(m + 1) * ldd + h * d + r] : decay[(m + 1) * ldd + h]) : 0.f;
+    }
+    if (more) {
+      vn = v[(m + 1) * ldv + h * e + c];
+      wn = wr[(m + 1) * ldw + h];
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RL; i++) {
+      s[i] *= ac[i];
+      if (DELTA) dot += s[i] * kc[i];
+    }
+    float u = wc * vc;
+    if (DELTA) u = wc * (vc - warp_sum(dot));
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < RL; i++) {
+      s[i] += kc[i] * u;
+      o += s[i] * qc[i];
+    }
+    o = warp_sum(o);
+    if (lane == 0) out[m * ldo + h * e + c] = o + sk * vc;
+#pragma unroll
+    for (int i = 0; i < RL; i++) { kc[i] = kn[i]; qc[i] = qn[i]; ac[i] = an[i]; }
+    vc = vn;
+    wc = wn;
+  }
+  if (sp) {
+#pragma unroll
+    for (int i = 0; i < RL; i++) {
+      const int r = lane + 32 * i;
+      if (r < d) sp[r] = s[i];
+    }
+  }
+}
+
+// out [M, H*e]; k, q [M, Gk*d] with the row stride ldk; v [M, H*e]; write [M, H]; decay [M, H*d] when
+// row_decay, else [M, H]; skip [H] or null; state [slots][H][e][d].  seq_qlen null: one row per sequence.
+LEB_API int leb_gated_recurrence(float* out, int ldo, const float* k, const float* q, int ldk, const float* v, int ldv,
+                                 const float* write, int ldw, const float* decay, int ldd, int row_decay, int delta,
+                                 const float* skip, float* state, const int* seq_slot, const int* seq_qstart,
+                                 const int* seq_qlen, int B, int H, int Gk, int d, int e, cudaStream_t st) {
+  if (B <= 0) return 0;
+  LEB_REQUIRE(H >= 1 && Gk >= 1 && H % Gk == 0, "leb_gated_recurrence: %d heads do not divide into %d key heads", H, Gk);
+  LEB_REQUIRE(d >= 1 && d <= 256 && e >= 1, "leb_gated_recurrence: a state of %d x %d (rows 1..256)", d, e);
+  LEB_REQUIRE(H <= 65535 && B <= 65535, "leb_gated_recurrence: step too large");
+  const dim3 grid(ceil_div(e, REC_WARPS), H, B), block(32 * REC_WARPS);
+  LebPlainLaunches plain(true);
+#define LEB_REC3(RL_, D_, R_) leb_launch(gated_recurrence_kernel<RL_, D_, R_>, grid, block, 0, st, out, ldo, k, q, ldk, v, ldv, \
+                                         write, ldw, decay, ldd, skip, state, seq_slot, seq_qstart, seq_qlen, H, Gk, d, e)
+#define LEB_REC2(RL_)                                     \
+  {                                                       \
+    if (delta && row_decay) LEB_REC3(RL_, true, true);    \
+    else if (delta) LEB_REC3(RL_, true, false);           \
+    else if (row_decay) LEB_REC3(RL_, false, true);       \
+    else LEB_REC3(RL_, false, false);                     \
+  }
+  if (d <= 32) LEB_REC2(1)
+  else if (d <= 64) LEB_REC2(2)
+  else if (d <= 128) LEB_REC2(4)
+  else LEB_REC2(8)
+#undef LEB_REC2
+#undef LEB_REC3
+  LEB_CHECK_LAUNCH("leb_gated_recurrence");
+  return 0;
+}
+
+// What a row of the delta-rule mixer needs between its convolutions and its recurrence, one block a row:
+//   q, k: silu, then unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale
+//   v: silu;  write = sigmoid(b);  decay = exp(-exp(A_log_h) softplus(a + dt_bias)) per head and key channel
+// qk [M, 2*Gk*d + H*e] is the convolution's output (q | k | v), `a` [M, H*d] the decay's pre-activation and
+// `b` [M, H] the write strength's (row strides lda, ldb).  Results: qn, kn [M, Gk*d], vs [M, H*e], g [M, H*d], wr [M, H].
+__global__ void __launch_bounds__(128)
+delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vs, float* __restrict__ g,
+                  float* __restrict__ wr, const float* __restrict__ qkv, int ldq, const float* __restrict__ a, int lda,
+                  const float* __restrict__ bw, int ldb, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                  int H, int Gk, int d, int e, float unit_eps, float q_scale) {
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* row = qkv + m * ldq;
+  for (int hh = warp; hh < 2 * Gk; hh += nw) {      // heads of q, then heads of k
+    const float* src = row + (size_t)hh * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float x = silu_f(src[i]);
+      ss += x * x;
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss + unit_eps) * (hh < Gk ? q_scale : 1.0f);
+    float* dst = hh < Gk ? qn + m * (size_t)(Gk * d) + (size_t)hh * d : kn + m * (size_t)(Gk * d) + (size_t)(hh - Gk) * d;
+    for (int i = lane; i < d; i += 32) dst[i] = silu_f(src[i]) * r;
+  }
+  const float* vrow = row + (size_t)2 * Gk * d;
+  for (int i = threadIdx.x; i < H * e; i += blockDim.x) vs[m * (size_t)(H * e) + i] = silu_f(vrow[i]);
+  for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+    const float rate = expf(A_log[i / d]);
+    g[m * (size_t)(H * d) + i] = expf(-rate * softplus_f(a[m * lda + i] + dt_bias[i]));
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) wr[m * H + i] = sigmoid_f(bw[m * ldb + i]);
+}
+
+LEB_API int leb_delta_prep(float* qn, float* kn, float* vs, float* g, float* wr, const float* qkv, int ldq, const float* a,
+                           int lda, const float* bw, int ldb, const float* dt_bias, const float* A_log, int M, int H, int Gk,
+                           int d, int e, float unit_eps, float q_scale, cudaStream_t st) {
+  if (M <= 0) return 0;
+  LebPlainLaunches plain(true);
+  leb_launch(delta_prep_kernel, dim3(M), dim3(128), 0, st, qn, kn, vs, g, wr, qkv, ldq, a, lda, bw, ldb, dt_bias, A_log,
+             H, Gk, d, e, unit_eps, q_scale);
+  LEB_CHECK_LAUNCH("leb_delta_prep");
+  return 0;
+}
+
+// What a row of the state-space mixer needs between its convolution and its recurrence:
+//   xbc <- silu(xbc + conv_bias) in place over the C convolved channels;
+//   dt = softplus(dt_raw + dt_bias) and decay = exp(-exp(A_log_h) dt), both [M, H].
+__global__ void __launch_bounds__(128)
+ssm_prep_kernel(float* __restrict__ xbc, int ldx, int C, const float* __restrict__ conv_bias, float* __restrict__ dt,
+                float* __restrict__ decay, const float* __restrict__ dt_raw, int ldt, const float* __restrict__ dt_bias,
+                const float* __restrict__ A_log, int H) {
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    const float x = xbc[m * ldx + i] + (conv_bias ? conv_bias[i] : 0.f);
+    xbc[m * ldx + i] = silu_f(x);
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float t = softplus_f(dt_raw[m * ldt + i] + dt_bias[i]);
+    dt[m * H + i] = t;
+    decay[m * H + i] = expf(-expf(A_log[i]) * t);
+  }
+}
+
+LEB_API int leb_ssm_prep(float* xbc, int ldx, int C, const float* conv_bias, float* dt, float* decay, const float* dt_raw,
+                         int ldt, const float* dt_bias, const float* A_log, int M, int H, cudaStream_t st) {
+  if (M <= 0) return 0;
+  LebPlainLaunches plain(true);
+  leb_launch(ssm_prep_kernel, dim3(M), dim3(128), 0, st, xbc, ldx, C, conv_bias, dt, decay, dt_raw, ldt, dt_bias, A_log, H);
+  LEB_CHECK_LAUNCH("leb_ssm_prep");
+  return 0;
+}
+
+// A recurrent mixer's result on its way to the output projection: groups of `gs` neighbouring numbers of a
+// row are divided by their root mean square (eps inside the root) and multiplied by a weight
+// (w[j % wlen]: one weight for every group, or one per column), and the row is gated by a second
+// row z: sigmoid(z) after the norm (gate_first = 0), or silu(z) before it (gate_first = 1).
+// y, z float; out in the activation type.  A warp takes a group.
+template <typename T>
+__global__ void __launch_bounds__(128)
+group_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ y, const float* __restrict__ z, int ldz,
+                       const float* __restrict__ w, int C, int gs, int wlen, float eps, int gate_first) {
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int gidx = warp; gidx < C / gs; gidx += nw) {
+    const float* yr = y + m * C + (size_t)gidx * gs;
+    const float* zr = z + m * ldz + (size_t)gidx * gs;
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) {
+      const float x = gate_first ? yr[i] * silu_f(zr[i]) : yr[i];
+      ss += x * x;
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int i = lane; i < gs; i += 32) {
+      const int j = gidx * gs + i;
+      const float x = gate_first ? yr[i] * silu_f(zr[i]) : yr[i];
+      float val = x * r * w[j % wlen];
+      if (!gate_first) val *= sigmoid_f(zr[i]);
+      out[m * C + j] = from_f32<T>(val);
+    }
+  }
+}
+
+LEB_API int leb_group_norm_gate(void* out, int dtype, const float* y, const float* z, int ldz, const float* w, int M, int C,
+                                int gs, int wlen, float eps, int gate_first, cudaStream_t st) {
+  if (M <= 0) return 0;
+  LEB_REQUIRE(gs >= 1 && C % gs == 0 && wlen >= 1, "leb_group_norm_gate: %d columns in groups of %d", C, gs);
+  LebPlainLaunches plain(true);
+  if (dtype == LEB_F32)
+    leb_launch(group_norm_gate_kernel<float>, dim3(M), dim3(128), 0, st, (float*)out, y, z, ldz, w, C, gs, wlen, eps, gate_first);
+  else if (dtype == LEB_BF16)
+    leb_launch(group_norm_gate_kernel<bf16>, dim3(M), dim3(128), 0, st, (bf16*)out, y, z, ldz, w, C, gs, wlen, eps, gate_first);
+  else
+    return leb_fail("leb_group_norm_gate: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_group_norm_gate");
+  return 0;
+}
+
+// ---- the post-norm layer arrangement and the embedding with learned positions ---------------------------
+// x <- LN(alpha x + y) with weight and bias (variance = mean of the squared deviations), one block a row;
+// with h, the same launch leaves the new row there in the activation type (the next sublayer's input).
+template <typename TH>
+__global__ void __launch_bounds__(512)
+postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ w,
+                         const float* __restrict__ bias, float eps, TH* __restrict__ h, int D) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float t = alpha * x[m * D + i] + y[m * D + i];
+    row[i] = t;
+    s += t;
+  }
+  const float mean = block_sum(s, red) / (float)D;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float dlt = row[i] - mean;
+    q += dlt * dlt;
+  }
+  const float r = 1.0f / sqrtf(block_sum(q, red) / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float t = (row[i] - mean) * r * w[i] + (bias ? bias[i] : 0.f);
+    x[m * D + i] = t;
+    if (h) h[m * D + i] = from_f32<TH>(t);
+  }
+}
+
+LEB_API int leb_postnorm_residual(float* x, const float* y, float alpha, const float* w, const float* bias, float eps,
+                                  void* h, int h_dtype, int M, int D, cudaStream_t st) {
+  if (M <= 0 || D <= 0) return 0;
+  LEB_REQUIRE((size_t)D * sizeof(float) <= 160 * 1024, "leb_postnorm_residual: a width of %d does not fit shared memory", D);
+  const size_t smem = (size_t)D * sizeof(float);
+  const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+  LebPlainLaunches plain(true);
+  static bool set = false;
+  if (smem > 48 * 1024 && !set) {
+    cudaFuncSetAttribute(postnorm_residual_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    cudaFuncSetAttribute(postnorm_residual_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    set = true;
+  }
+  if (!h || h_dtype == LEB_F32)
+    leb_launch(postnorm_residual_kernel<float>, dim3(M), dim3(threads), smem, st, x, y, alpha, w, bias, eps, (float*)h, D);
+  else if (h_dtype == LEB_BF16)
+    leb_launch(postnorm_residual_kernel<bf16>, dim3(M), dim3(threads), smem, st, x, y, alpha, w, bias, eps, (bf16*)h, D);
+  else
+    return leb_fail("leb_postnorm_residual: unknown dtype %d", h_dtype);
+  LEB_CHECK_LAUNCH("leb_postnorm_residual");
+  return 0;
+}
+
+// out[r] = LN(x[rows[r]]) * w + bias (rows null: the rows as they come); x float, out any activation type.
+template <typename T>
+__global__ void __launch_bounds__(512)
+layernorm_bias_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                      const float* __restrict__ bias, const int* __restrict__ rows, int D, float eps) {
+  __shared__ float red[33];
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[m] : m) * D;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) s += xr[i];
+  const float mean = block_sum(s, red) / (float)D;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float dlt = xr[i] - mean;
+    q += dlt * dlt;
+  }
+  const float r = 1.0f / sqrtf(block_sum(q, red) / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x)
+    out[m * D + i] = from_f32<T>((xr[i] - mean) * r * w[i] + (bias ? bias[i] : 0.f));
+}
+
+LEB_API int leb_layernorm_bias(void* out, int dtype, const float* x, const float* w, const float* bias, const int* rows,
+                               int M, int D, float eps, cudaStream_t st) {
+  if (M <= 0 || D <= 0) return 0;
+  const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+  LebPlainLaunches plain(true);
+  if (dtype == LEB_F32)
+    leb_launch(layernorm_bias_kernel<float>, dim3(M), dim3(threads), 0, st, (float*)out, x, w, bias, rows, D, eps);
+  else if (dtype == LEB_BF16)
+    leb_launch(layernorm_bias_kernel<bf16>, dim3(M), dim3(threads), 0, st, (bf16*)out, x, w, bias, rows, D, eps);
+  else
+    return leb_fail("leb_layernorm_bias: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_layernorm_bias");
+  return 0;
+}
+
+// x[m] = table[token[m]] * scale + positions[row_pos[m]] as float; with h, the row in the activation type too.
+template <typename T, typename TH>
+__global__ void __launch_bounds__(256)
+embed_positions_kernel(float* __restrict__ x, TH* __restrict__ h, const T* __restrict__ table, const int* __restrict__ tokens,
+                       const float* __restrict__ positions, const int* __restrict__ row_pos, int D, int V, int n_pos,
+                       float scale) {
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  int tok = tokens[m];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  int p = row_pos[m];
+  p = p < 0 ? 0 : (p >= n_pos ? n_pos - 1 : p);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float t = to_f32(table[(size_t)tok * D + i]) * scale + positions[(size_t)p * D + i];
+    x[m * D + i] = t;
+    if (h) h[m * D + i] = from_f32<TH>(t);
+  }
+}
+
+LEB_API int leb_embed_positions(float* x, void* h, int h_dtype, const void* table, int dtype, const int* tokens,
+                                const float* positions, const int* row_pos, int M, int D, int V, int n_pos, float scale,
+                                cudaStream_t st) {
+  if (M <= 0) return 0;
+  LEB_REQUIRE(dtype == LEB_F32 || dtype == LEB_BF16, "leb_embed_positions: unknown dtype %d", dtype);
+  LebPlainLaunches plain(true);
+  const dim3 grid(M), block(256);
+  if (dtype == LEB_F32)
+    leb_launch(embed_positions_kernel<float, float>, grid, block, 0, st, x, (float*)h, (const float*)table, tokens, positions,
+               row_pos, D, V, n_pos, scale);
+  else if (!h || h_dtype == LEB_BF16)
+    leb_launch(embed_positions_kernel<bf16, bf16>, grid, block, 0, st, x, (bf16*)h, (const bf16*)table, tokens, positions,
+               row_pos, D, V, n_pos, scale);
+  else
+    leb_launch(embed_positions_kernel<bf16, float>, grid, block, 0, st, x, (float*)h, (const bf16*)table, tokens, positions,
+               row_pos, D, V, n_pos, scale);
+  LEB_CHECK_LAUNCH("leb_embed_positions");
+  return 0;
+}
+
+// out[i] = cast(x[i]): the residual stream in the activation type, for a sublayer that reads the stream itself.
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ out, const float* __restrict__ x, size_t n) {
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_f32<T>(x[i]);
+}
+
+LEB_API int leb_cast_rows(void* out, int dtype, const float* x, size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  LebPlainLaunches plain(true);
+  const dim3 grid((unsigned)((n + 255) / 256)), block(256);
+  if (dtype == LEB_F32) leb_launch(cast_rows_kernel<float>, grid, block, 0, st, (float*)out, x, n);
+  else if (dtype == LEB_BF16) leb_launch(cast_rows_kernel<bf16>, grid, block, 0, st, (bf16*)out, x, n);
+  else return leb_fail("leb_cast_rows: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_cast_rows");
+  return 0;
+}

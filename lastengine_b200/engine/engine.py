@@ -15,7 +15,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
-from ..cache import Cache, CacheError
+from ..cache import Cache, CacheError, pooled_table_key
 from ..config.base import read_config_json
 from ..parts.base import BuildEnv, ModelPlan
 from ..registry import plan_from_config
@@ -165,6 +165,9 @@ class Engine:
                     pos0.append(self.cache.length(s))
                 except CacheError:
                     raise StepError(f"sequence {s} is not live (never started, or already released)") from None
+                limit = self.plan.max_positions
+                if limit is not None and pos0[-1] + len(t) > limit:
+                    raise StepError(f"sequence {s} would reach {pos0[-1] + len(t)} positions, the model takes {limit}")
                 ta = np.asarray(t)
                 if ta.min() < 0 or ta.max() >= V:
                     bad = int(ta[(ta < 0) | (ta >= V)][0])
@@ -203,6 +206,9 @@ class Engine:
         for gi, g in enumerate(self.cache.kv_groups):
             width = table_width or max(1, max((len(g.seq_pages.get(s, ())) for s in live), default=1))
             tables[gi] = g.table(list(seqs), width)
+            if g.pool > 0:      # the page lists of the pooled rows: never longer than those of the positions
+                pw = table_width or max(1, max((len(g.seq_pooled_pages.get(s, ())) for s in live), default=1))
+                tables[pooled_table_key(gi)] = g.table(list(seqs), pw, pooled=True)
         b = (builder or self.builder).build(list(seqs), tokens, pos0, rows, tables, u01=u01, feed=feed)
         return b, grow
 

@@ -143,8 +143,8 @@ class DecodeGraph:
         eng, bb = self.engine, self.builder
         if self.batch is None or slots != self.staged_slots or eng.cache.state_version != self.cache_version:
             return None
-        if any(g.spec.window > 0 for g in eng.cache.kv_groups):
-            return None      # windowed groups give pages back as they go: stage those steps in full
+        if any(g.spec.window > 0 or g.pool > 0 for g in eng.cache.kv_groups):
+            return None      # windowed groups give pages back as they go (and pooled rows get pages): stage those steps in full
         cache = eng.cache
         n = len(slots)
         page = cache.page_size

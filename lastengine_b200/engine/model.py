@@ -95,11 +95,11 @@ class Model:
         env, ws = self.env, self.env.workspace
         M, D = batch.n_rows, self.hidden_size
         x = ws.get("model.x", (M, D), torch.float32)
-        self.embedding.forward(x, batch.tokens)
+        self.embedding.forward(x, batch.tokens, batch=batch)
         x0 = None
         if self.keeps_embedding:      # the embedding output is added to the stream again later
             x0 = ws.get("model.x0", (M, D), torch.float32)
-            self.embedding.forward(x0, batch.tokens)
+            self.embedding.forward(x0, batch.tokens, batch=batch)
         sched = self.plan.schedule
         pending = None      # the half of the next block's first norm that the last block left (decode steps)
         for i, e in enumerate(sched):

@@ -150,6 +150,17 @@ def _declare(L) -> None:
         "leb_selftest_bounded_wait": [P, I, I, P],
         "leb_gemm_bf16_tc_slices": [I, I, I],
         "leb_gemm_bf16_tc_sliced": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
+        "leb_gated_recurrence": [P, I, P, P, I, P, I, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, P],
+        "leb_delta_prep": [P, P, P, P, P, P, I, P, I, P, I, P, P, I, I, I, I, I, F, F, P],
+        "leb_ssm_prep": [P, I, I, P, P, P, P, I, P, P, I, I, P],
+        "leb_group_norm_gate": [P, I, P, P, I, P, I, I, I, I, F, I, P],
+        "leb_postnorm_residual": [P, P, F, P, P, F, P, I, I, I, P],
+        "leb_layernorm_bias": [P, I, P, P, P, P, I, I, F, P],
+        "leb_embed_positions": [P, P, I, P, I, P, P, P, I, I, I, I, F, P],
+        "leb_cast_rows": [P, I, P, S, P],
+        "leb_pooled_attn_prep": [P, P, P, I, P, I, P, P, P, F, P, I, P, P, I, P, P, P, I, I, I, I, I, I, P],
+        "leb_pool_blocks": [P, P, P, P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, I, P],
+        "leb_attention_pooled": [P, P, P, P, P, I, P, I, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -243,8 +254,24 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float,
                              float(eps), 1 if add else 0, _stream()))
 
 
-def layernorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
-    """out = (x - mean) / sqrt(var + eps) * w per row (no bias); x is float."""
+def layernorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float, rows: torch.Tensor | None = None,
+              bias: torch.Tensor | None = None) -> None:
+    """out = (x - mean) / sqrt(var + eps) * w (+ bias) per row; x is float."""
+    if bias is not None:
+        _cuda(out, "layernorm.out")
+        _cuda(x, "layernorm.x", torch.float32)
+        _cuda(w, "layernorm.w", torch.float32)
+        _cuda(bias, "layernorm.bias", torch.float32)
+        M, D = out.shape
+        assert x.shape[1] == D and w.numel() == D and bias.numel() == D
+        if rows is not None:
+            _cuda(rows, "layernorm.rows", torch.int32)
+            assert rows.numel() >= M
+        else:
+            assert x.shape[0] >= M
+        _check(lib().leb_layernorm_bias(_ptr(out), _dt(out, "layernorm.out"), _ptr(x), _ptr(w), _ptr(bias), _ptr(rows),
+                                        M, D, float(eps), _stream()))
+        return
     _cuda(out, "layernorm.out")
     _cuda(x, "layernorm.x", torch.float32)
     _cuda(w, "layernorm.w", torch.float32)
@@ -272,6 +299,239 @@ def scaled_residual(x: torch.Tensor, y: torch.Tensor, mult: float, h: torch.Tens
         assert h.shape == (M, D) and norm_w.numel() == D
     _check(lib().leb_scaled_residual(_ptr(x), _ptr(y), float(mult), _ptr(h), _dt(h, "scaled_residual.h") if h is not None else F32,
                                      _ptr(norm_w), float(eps), M, D, _stream()))
+
+
+def postnorm_residual(x: torch.Tensor, y: torch.Tensor, alpha: float, w: torch.Tensor, bias: torch.Tensor | None,
+                      eps: float, h: torch.Tensor | None = None) -> None:
+    """x <- LN(alpha x + y) * w + bias per row (x, y float [M, D]); with `h` [M, D] the launch also leaves the
+    new rows there in h's type (the input of the sublayer that reads the stream next)."""
+    _cuda(x, "postnorm_residual.x", torch.float32)
+    _cuda(y, "postnorm_residual.y", torch.float32)
+    _cuda(w, "postnorm_residual.w", torch.float32)
+    M, D = x.shape
+    assert y.shape == (M, D) and w.numel() == D
+    if bias is not None:
+        _cuda(bias, "postnorm_residual.bias", torch.float32)
+        assert bias.numel() == D
+    if h is not None:
+        _cuda(h, "postnorm_residual.h")
+        assert h.shape == (M, D)
+    _check(lib().leb_postnorm_residual(_ptr(x), _ptr(y), float(alpha), _ptr(w), _ptr(bias), float(eps), _ptr(h),
+                                       _dt(h, "postnorm_residual.h") if h is not None else F32, M, D, _stream()))
+
+
+def embed_positions(x: torch.Tensor, h: torch.Tensor | None, table: torch.Tensor, tokens: torch.Tensor,
+                    positions: torch.Tensor, row_pos: torch.Tensor, scale: float = 1.0) -> None:
+    """x[m] = table[tokens[m]] * scale + positions[row_pos[m]] as float; with `h`, the rows in h's type too."""
+    _cuda(x, "embed_positions.x", torch.float32)
+    _cuda(table, "embed_positions.table")
+    _cuda(tokens, "embed_positions.tokens", torch.int32)
+    _cuda(positions, "embed_positions.positions", torch.float32)
+    _cuda(row_pos, "embed_positions.row_pos", torch.int32)
+    M, D = x.shape
+    assert table.shape[1] == D and positions.shape[1] == D and tokens.numel() >= M and row_pos.numel() >= M
+    if h is not None:
+        _cuda(h, "embed_positions.h")
+        assert h.shape == (M, D)
+    _check(lib().leb_embed_positions(_ptr(x), _ptr(h), _dt(h, "embed_positions.h") if h is not None else F32, _ptr(table),
+                                     _dt(table, "embed_positions.table"), _ptr(tokens), _ptr(positions), _ptr(row_pos),
+                                     M, D, table.shape[0], positions.shape[0], float(scale), _stream()))
+
+
+def cast_rows(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out = x in out's type (x float, both contiguous and of one shape)."""
+    _cuda(out, "cast_rows.out")
+    _cuda(x, "cast_rows.x", torch.float32)
+    assert out.numel() == x.numel()
+    _check(lib().leb_cast_rows(_ptr(out), _dt(out, "cast_rows.out"), _ptr(x), x.numel(), _stream()))
+
+
+def _f32_rows(t: torch.Tensor, name: str, M: int, width: int) -> int:
+    """Checks a float [M, width] tensor that may be a column slice; returns its row stride."""
+    _cuda(t, name, torch.float32, contiguous=False)
+    assert t.shape == (M, width) and (width == 0 or t.stride(1) == 1), f"{name}: {tuple(t.shape)}, expected {(M, width)}"
+    return t.stride(0)
+
+
+def delta_prep(qn: torch.Tensor, kn: torch.Tensor, vs: torch.Tensor, g: torch.Tensor, wr: torch.Tensor, qkv: torch.Tensor,
+               a: torch.Tensor, b: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, H: int, Gk: int, d: int, e: int,
+               unit_eps: float, q_scale: float) -> None:
+    """Between the convolutions and the recurrence of a delta-rule mixer (all float): q and k = silu, then unit
+    vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale; v = silu; write strength sigmoid(b);
+    decay exp(-exp(A_log_h) softplus(a + dt_bias)) per head and key channel.  qkv [M, 2 Gk d + H e] holds the
+    convolved q | k | v; a [M, H d] and b [M, H] may be column slices."""
+    M = qn.shape[0]
+    for t, n, w in ((qn, "qn", Gk * d), (kn, "kn", Gk * d), (vs, "vs", H * e), (g, "g", H * d), (wr, "wr", H)):
+        _cuda(t, f"delta_prep.{n}", torch.float32)
+        assert t.shape == (M, w)
+    ldq = _f32_rows(qkv, "delta_prep.qkv", M, 2 * Gk * d + H * e)
+    lda = _f32_rows(a, "delta_prep.a", M, H * d)
+    ldb = _f32_rows(b, "delta_prep.b", M, H)
+    _cuda(dt_bias, "delta_prep.dt_bias", torch.float32)
+    _cuda(A_log, "delta_prep.A_log", torch.float32)
+    assert dt_bias.numel() == H * d and A_log.numel() == H
+    _check(lib().leb_delta_prep(_ptr(qn), _ptr(kn), _ptr(vs), _ptr(g), _ptr(wr), _ptr(qkv), ldq, _ptr(a), lda, _ptr(b), ldb,
+                                _ptr(dt_bias), _ptr(A_log), M, H, Gk, d, e, float(unit_eps), float(q_scale), _stream()))
+
+
+def ssm_prep(xbc: torch.Tensor, conv_bias: torch.Tensor | None, dt: torch.Tensor, decay: torch.Tensor, dt_raw: torch.Tensor,
+             dt_bias: torch.Tensor, A_log: torch.Tensor) -> None:
+    """Between the convolution and the recurrence of a state-space mixer (all float): xbc <- silu(xbc + conv_bias)
+    in place; dt = softplus(dt_raw + dt_bias) and decay = exp(-exp(A_log_h) dt), both [M, H]."""
+    M, C = xbc.shape
+    H = dt.shape[1]
+    ldx = _f32_rows(xbc, "ssm_prep.xbc", M, C)
+    ldt = _f32_rows(dt_raw, "ssm_prep.dt_raw", M, H)
+    for t, n in ((dt, "dt"), (decay, "decay")):
+        _cuda(t, f"ssm_prep.{n}", torch.float32)
+        assert t.shape == (M, H)
+    for t, n, w in ((conv_bias, "conv_bias", C), (dt_bias, "dt_bias", H), (A_log, "A_log", H)):
+        if t is not None:
+            _cuda(t, f"ssm_prep.{n}", torch.float32)
+            assert t.numel() == w
+    _check(lib().leb_ssm_prep(_ptr(xbc), ldx, C, _ptr(conv_bias), _ptr(dt), _ptr(decay), _ptr(dt_raw), ldt, _ptr(dt_bias),
+                              _ptr(A_log), M, H, _stream()))
+
+
+RECURRENCE_MAX_ROWS = 256     # rows of a head's state the recurrence kernel takes
+
+
+def gated_recurrence(out: torch.Tensor, k: torch.Tensor, q: torch.Tensor, v: torch.Tensor, write: torch.Tensor,
+                     decay: torch.Tensor, state: torch.Tensor, batch, H: int, Gk: int, d: int, e: int,
+                     delta: bool, skip: torch.Tensor | None = None) -> None:
+    """The linear recurrence of the step's rows with a state per sequence and head (all float):
+        S <- diag(decay) S;  u = write * v (delta: write * (v - S^T k));  S <- S + k u^T;  o = S^T q (+ skip_h v)
+    k, q [M, Gk*d] (one row stride), v [M, H*e], write [M, H], decay [M, H*d] (per key channel) or [M, H];
+    head h reads key head h // (H // Gk); state [slots, H, e, d] (a column of S is contiguous); out [M, H*e]."""
+    M = out.shape[0]
+    ldo = _f32_rows(out, "gated_recurrence.out", M, H * e)
+    ldk = _f32_rows(k, "gated_recurrence.k", M, Gk * d)
+    assert _f32_rows(q, "gated_recurrence.q", M, Gk * d) == ldk
+    ldv = _f32_rows(v, "gated_recurrence.v", M, H * e)
+    ldw = _f32_rows(write, "gated_recurrence.write", M, H)
+    row_decay = decay.shape[1] == H * d and not (d == 1 and decay.shape[1] == H and False)
+    if decay.shape[1] != H * d:
+        row_decay = False
+    ldd = _f32_rows(decay, "gated_recurrence.decay", M, H * d if row_decay else H)
+    _cuda(state, "gated_recurrence.state", torch.float32)
+    assert state.shape[1:] == (H, e, d)
+    if skip is not None:
+        _cuda(skip, "gated_recurrence.skip", torch.float32)
+        assert skip.numel() == H
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_gated_recurrence(_ptr(out), ldo, _ptr(k), _ptr(q), ldk, _ptr(v), ldv, _ptr(write), ldw, _ptr(decay), ldd,
+                                      1 if row_decay else 0, 1 if delta else 0, _ptr(skip), _ptr(state), _ptr(batch.seq_slot),
+                                      _ptr(batch.seq_qstart), None if single else _ptr(batch.seq_qlen), batch.n_seqs,
+                                      H, Gk, d, e, _stream()))
+
+
+def group_norm_gate(out: torch.Tensor, y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, group_size: int, eps: float,
+                    gate_first: bool) -> None:
+    """Groups of `group_size` neighbouring numbers of a row of y (float [M, C]) divided by their root mean square,
+    times w[j % len(w)], gated by z (float [M, C], a column slice is fine): times sigmoid(z) after the norm, or
+    (gate_first) y silu(z) before it.  out [M, C] in the activation type."""
+    _cuda(out, "group_norm_gate.out")
+    M, C = out.shape
+    _cuda(y, "group_norm_gate.y", torch.float32)
+    assert y.shape == (M, C)
+    ldz = _f32_rows(z, "group_norm_gate.z", M, C)
+    _cuda(w, "group_norm_gate.w", torch.float32)
+    _check(lib().leb_group_norm_gate(_ptr(out), _dt(out, "group_norm_gate.out"), _ptr(y), _ptr(z), ldz, _ptr(w), M, C,
+                                     int(group_size), w.numel(), float(eps), 1 if gate_first else 0, _stream()))
+
+
+def pooled_attn_prep(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, proj: torch.Tensor,
+                     bias: torch.Tensor | None, q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, eps: float,
+                     freq_qk: torch.Tensor | None, rot: int, freq_v: torch.Tensor | None, block_table: torch.Tensor, batch,
+                     nh: int, nkv: int, hd: int, vd: int, page_size: int) -> None:
+    """The step's rows on their way into the windowed attention with rotated values: proj (float [M, (nh + nkv) hd +
+    nkv vd], q | k | v) plus bias; q and k heads RMS-normed with a weight and rotated on their first `rot` numbers
+    (split-half pairs, position * freq_qk); v heads rotated over their whole width (position * freq_v); q to q_out,
+    k and v to the cache."""
+    _cuda(q_out, "pooled_attn_prep.q_out")
+    M = q_out.shape[0]
+    assert q_out.shape == (M, nh * hd)
+    ldp = _f32_rows(proj, "pooled_attn_prep.proj", M, (nh + nkv) * hd + nkv * vd)
+    _cuda(k_pool, "pooled_attn_prep.k_pool", q_out.dtype)
+    _cuda(v_pool, "pooled_attn_prep.v_pool", q_out.dtype)
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, vd, page_size)
+    _cuda(block_table, "pooled_attn_prep.block_table", torch.int32)
+    for name, t, n in (("bias", bias, proj.shape[1]), ("q_norm_w", q_norm_w, hd), ("k_norm_w", k_norm_w, hd),
+                       ("freq_qk", freq_qk, rot // 2), ("freq_v", freq_v, vd // 2)):
+        if t is not None:
+            _cuda(t, f"pooled_attn_prep.{name}", torch.float32)
+            assert t.numel() == n, f"pooled_attn_prep.{name}: {t.numel()} numbers, expected {n}"
+    _check(lib().leb_pooled_attn_prep(_ptr(q_out), _ptr(k_pool), _ptr(v_pool), _dt(q_out, "pooled_attn_prep"), _ptr(proj), ldp,
+                                      _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(freq_qk), int(rot) if freq_qk is not None else 0,
+                                      _ptr(freq_v), _ptr(block_table), block_table.shape[1], _ptr(batch.row_seq),
+                                      _ptr(batch.row_pos), _ptr(batch.seq_slot), M, nh, nkv, hd, vd, page_size, _stream()))
+
+
+def pool_blocks(pk_pool: torch.Tensor, pv_pool: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                block_table: torch.Tensor, pool_table: torch.Tensor, batch, nkv: int, hd: int, vd: int, page_size: int,
+                pool: int) -> None:
+    """The pooled key and value (means over `pool` cached positions) of every block whose last position is among
+    the step's rows, into the pooled pools at the block's number."""
+    for t, n in ((pk_pool, "pk_pool"), (pv_pool, "pv_pool"), (v_pool, "v_pool")):
+        _cuda(t, f"pool_blocks.{n}", k_pool.dtype)
+    _cuda(k_pool, "pool_blocks.k_pool")
+    assert pk_pool.shape[1:] == (nkv, page_size, hd) and pv_pool.shape[1:] == (nkv, vd, page_size)
+    single = batch.max_qlen == 1 and batch.n_rows == batch.n_seqs
+    _check(lib().leb_pool_blocks(_ptr(pk_pool), _ptr(pv_pool), _ptr(k_pool), _ptr(v_pool), _dt(k_pool, "pool_blocks"),
+                                 _ptr(block_table), block_table.shape[1], _ptr(pool_table), pool_table.shape[1],
+                                 _ptr(batch.seq_slot), _ptr(batch.seq_pos0), None if single else _ptr(batch.seq_qlen),
+                                 batch.n_seqs, batch.max_qlen, nkv, hd, vd, page_size, int(pool), _stream()))
+
+
+def pooled_attention_splits(batch, nkv: int, G: int, window: int, pool: int) -> int:
+    """Blocks that share one sequence's key range in a decode step (1 for prompts): the range is the window plus
+    the pooled blocks behind it; a split gets 128 keys or more, and no more blocks are made than run at once."""
+    if batch.max_qlen != 1:
+        return 1
+    kv = max(int(batch.max_kvlen), 1)
+    keys = min(kv, window) + (max(0, kv - window) // pool if pool > 0 else 0) if window > 0 else kv
+    per = max(batch.n_seqs * nkv * ((G + 7) // 8), 1)
+    return max(1, min(keys // 128, (4 * sm_count()) // per, 16))
+
+
+def attention_pooled(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                     pk_pool: torch.Tensor | None, pv_pool: torch.Tensor | None, pool_table: torch.Tensor | None, batch,
+                     head_scale: torch.Tensor, freq_v: torch.Tensor | None, nh: int, nkv: int, hd: int, vd: int,
+                     page_size: int, window: int, pool: int, n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """Attention of the step's rows inside a window of `window` positions plus one pooled key and value for every
+    block of `pool` positions wholly before the window (one softmax over both), scores times head_scale[h];
+    the heads' results are turned back by their row's position (values are cached rotated) when freq_v is given."""
+    _cuda(out, "attention_pooled.out")
+    M = out.shape[0]
+    _cuda(q, "attention_pooled.q", out.dtype)
+    assert out.shape == (M, nh * vd) and q.shape == (M, nh * hd)
+    _cuda(k_pool, "attention_pooled.k_pool", out.dtype)
+    _cuda(v_pool, "attention_pooled.v_pool", out.dtype)
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, vd, page_size)
+    _cuda(block_table, "attention_pooled.block_table", torch.int32)
+    pt_width = 0
+    if pool > 0:
+        _cuda(pk_pool, "attention_pooled.pk_pool", out.dtype)
+        _cuda(pv_pool, "attention_pooled.pv_pool", out.dtype)
+        _cuda(pool_table, "attention_pooled.pool_table", torch.int32)
+        assert pk_pool.shape[1:] == (nkv, page_size, hd) and pv_pool.shape[1:] == (nkv, vd, page_size)
+        pt_width = pool_table.shape[1]
+    _cuda(head_scale, "attention_pooled.head_scale", torch.float32)
+    assert head_scale.numel() == nh
+    if freq_v is not None:
+        _cuda(freq_v, "attention_pooled.freq_v", torch.float32)
+        assert freq_v.numel() == vd // 2
+    if n_splits > 1:
+        need = M * nh * n_splits * (vd + 2)
+        if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"attention_pooled: {n_splits} splits need {need} floats of scratch")
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_attention_pooled(
+        _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention_pooled"), _ptr(block_table),
+        block_table.shape[1], _ptr(pk_pool) if pool > 0 else None, _ptr(pv_pool) if pool > 0 else None,
+        _ptr(pool_table) if pool > 0 else None, pt_width, _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart),
+        None if single else _ptr(batch.seq_qlen), _ptr(batch.row_pos), _ptr(head_scale), _ptr(freq_v), M, batch.n_seqs,
+        nh, nkv, hd, vd, page_size, int(window), int(pool), batch.max_qlen, int(n_splits), _stream()))
 
 
 def swiglu(out: torch.Tensor, gu: torch.Tensor) -> None:
@@ -1008,10 +1268,14 @@ _OPTIONAL_TC: list = [None]
 
 # ----------------------------------------------------------------------------------------------
 def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr: torch.Tensor,
-               bias: torch.Tensor | None, norm_topk: bool, scaling: float, softmax_chosen: bool = False) -> None:
+               bias: torch.Tensor | None, norm_topk: bool, scaling: float, softmax_chosen: bool = False,
+               softmax_groups: tuple[int, int] | None = None) -> None:
     """The k experts of every row and their weights.  Default: sigmoid scores, the bias only chooses,
     weights are the chosen sigmoids (over their sum with norm_topk).  `softmax_chosen`: logits Wr h + bias,
-    the k largest chosen, weights the softmax over the chosen logits alone."""
+    the k largest chosen, weights the softmax over the chosen logits alone.  `softmax_groups` = (groups, keep):
+    scores are the softmax over all experts, the bias only chooses, only experts of the `keep` best of
+    `groups` equal groups of neighbours (a group's score: its largest choice score) can be chosen, weights
+    are the chosen scores over their sum (+ 1e-20)."""
     _cuda(topk_ids, "moe_router.topk_ids", torch.int32)
     _cuda(topk_w, "moe_router.topk_w", torch.float32)
     _cuda(h, "moe_router.h")
@@ -1022,8 +1286,14 @@ def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr
     if bias is not None:
         _cuda(bias, "moe_router.bias", torch.float32)
         assert bias.numel() == E
+    mode = 2 if softmax_chosen else (1 if norm_topk else 0)
+    if softmax_groups is not None:
+        groups, keep = int(softmax_groups[0]), int(softmax_groups[1])
+        if not (1 <= keep <= groups <= 255 and E % groups == 0 and keep * (E // groups) >= k):
+            raise KernelError(f"moe_router: {keep} of {groups} groups over {E} experts cannot give {k} choices")
+        mode = 3 | (groups << 8) | (keep << 16)
     _check(lib().leb_moe_router(_ptr(topk_ids), _ptr(topk_w), _ptr(h), _dt(h, "moe_router.h"), _ptr(wr),
-                                _ptr(bias), M, D, E, k, 2 if softmax_chosen else (1 if norm_topk else 0), float(scaling), _stream()))
+                                _ptr(bias), M, D, E, k, mode, float(scaling), _stream()))
 
 
 def moe_align(offsets: torch.Tensor, sorted_pair: torch.Tensor, pair_row: torch.Tensor,

@@ -13,8 +13,8 @@ Every part:
     load(tensors, env)                             takes its tensors (already on the device,
                                                    in the dtype of their role) and may fuse them
 Mixer:
-    cache_spec() -> KVSpec | LatentSpec | StateSpec what it keeps per sequence (or a tuple of one
-                    | (KVSpec, StateSpec) | None    KVSpec and one StateSpec for a mixer that keeps both)
+    cache_spec() -> KVSpec | LatentSpec | StateSpec what it keeps per sequence (or a tuple of at most one
+                    | (KVSpec, StateSpec, ...) | None KVSpec and any states of different shapes)
     forward(h, out, accumulate, batch, cache, env) h: [rows, hidden] normed input in the
                                                    activation dtype; writes (or adds) its
                                                    result into the float tensor `out`
@@ -54,16 +54,30 @@ class TensorSpec:
     optional: bool = False        # may be absent from the checkpoint
     shared_name: str | None = None  # the tensor's full name where it belongs to the model, not to the
                                     # part's prefix (several parts may then name the same tensor)
+    free: int | None = None       # a size the checkpoint decides stands as -1 in `shape`; random weights take this one
+
+    def fits(self, found: tuple[int, ...]) -> bool:
+        """Whether a stored tensor of shape `found` is one of this spec (-1 takes any size)."""
+        return len(found) == len(self.shape) and all(s in (-1, int(f)) for s, f in zip(self.shape, found))
+
+    def concrete_shape(self) -> tuple[int, ...]:
+        """The shape random weights are made with."""
+        if -1 in self.shape and self.free is None:
+            raise ValueError(f"a tensor of shape {self.shape} has a size only a checkpoint gives")
+        return tuple(self.free if s == -1 else s for s in self.shape)
 
 
 @dataclass(frozen=True)
 class KVSpec:
     """Keys and values that grow with the sequence; `window` > 0 keeps only the last ones.
-    `v_head_dim`: width of a value head where it differs from a key head's (None: the same)."""
+    `v_head_dim`: width of a value head where it differs from a key head's (None: the same).
+    `pool` > 0: beside them one pooled key and value row for every complete block of `pool` positions,
+    in pages of their own (block b in row b); they stay when the window has let the block's positions go."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int | None = None
+    pool: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -162,6 +176,7 @@ class ModelPlan:
                                            # model has no use for (an optional tensor of a part no layer has): skipped
     stream_adds: tuple[StreamAdd, ...] = ()     # additions to the residual stream between schedule entries
     stream_tables: dict[str, tuple[int, ...]] = field(default_factory=dict)   # canonical name -> shape of their tables
+    max_positions: int | None = None   # the longest sequence the model takes (a table of learned positions); None: no limit
     checkpoint_names: Any = None   # callable: canonical name -> name in a checkpoint (the inverse of
                                    # tensor_aliases; None: "model." in front of everything but the head)
 

@@ -241,3 +241,75 @@ class ParallelResidualBlock:
         h2 = ws.get("block.h2" if h is ws.get("block.h", (M, D), env.dtype) else "block.h", (M, D), env.dtype)
         kernels.scaled_residual(x, y, self.mult, h=h2, norm_w=after.weight, eps=after.eps)
         return NormedRows(h2, after)
+
+
+class StreamRows:
+    """The residual stream in the activation type, as a block left it for a block that reads the stream itself."""
+
+    filled = False      # not the half of a split norm
+    norm = None
+
+    def __init__(self, values: torch.Tensor):
+        self.values = values
+
+
+@BLOCKS.register("post_norm_residual")
+class PostNormResidualBlock:
+    """x <- norm1(alpha x + Mixer(x));  x <- norm2(alpha x + FeedForward(x)): the sublayers read the stream
+    itself and the norm comes after each sum, with a constant `alpha` on the stream's side of it.  A layer may
+    have no feed-forward: it then ends after the first norm.  The stream, the sums and the norms are float; the
+    sublayers get the stream in the activation type.  The kernel that norms a sum also leaves the new stream in
+    the activation type for the sublayer that reads it next (in this block, or the first of the next block when
+    that is of this arrangement too and nothing is added to the stream in between), so the stream is cast by a
+    kernel of its own only in front of the model's first layer."""
+
+    def __init__(self, mixer, ffn, mixer_norm, ffn_norm=None, post_mixer_norm=None, post_ffn_norm=None,
+                 alpha: float = 1.0):
+        if post_mixer_norm is not None or post_ffn_norm is not None:
+            raise ValueError("the post-norm arrangement names its two norms mixer_norm and ffn_norm")
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        for n in (mixer_norm, ffn_norm):
+            if n is not None and not hasattr(n, "bias"):
+                raise ValueError("the post-norm arrangement takes layer norms")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+        self.alpha = float(alpha)
+
+    def parts(self) -> dict[str, object]:
+        p = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.ffn is not None:
+            p["ffn"], p["ffn_norm"] = self.ffn, self.ffn_norm
+        return p
+
+    def first_reader(self):
+        """(norm, reader): no norm stands in front of this block; the reader is the block itself, so a
+        block of this arrangement before it leaves the stream in the activation type."""
+        return None, self
+
+    def forward(self, x: torch.Tensor, batch, cache, env, pending=None):
+        M, D = x.shape
+        ws = env.workspace
+        env.split_in = env.split_out = None
+        f32 = env.is_float32
+        if f32:
+            h = x        # the sublayers read the stream where it is; they write elsewhere
+        elif isinstance(pending, StreamRows) and pending.values.shape == (M, D):
+            h = pending.values
+        else:
+            h = ws.get("block.h", (M, D), env.dtype)
+            kernels.cast_rows(h, x)
+        other = None if f32 else ws.get("block.h2" if h is ws.get("block.h", (M, D), env.dtype) else "block.h", (M, D), env.dtype)
+        nxt = env.next_block_norm
+        feeds_next = (not f32) and nxt is not None and isinstance(nxt[1], PostNormResidualBlock)
+        y = ws.get("block.t", (M, D), torch.float32)
+        self.mixer.forward(h, y, False, batch, cache, env)
+        n1 = self.mixer_norm
+        if self.ffn is None:
+            kernels.postnorm_residual(x, y, self.alpha, n1.weight, n1.bias, n1.eps, h=other if feeds_next else None)
+            return StreamRows(other) if feeds_next else None
+        kernels.postnorm_residual(x, y, self.alpha, n1.weight, n1.bias, n1.eps, h=other)
+        h2 = x if f32 else other
+        self.ffn.forward(h2, y, False, batch, env)
+        n2 = self.ffn_norm
+        kernels.postnorm_residual(x, y, self.alpha, n2.weight, n2.bias, n2.eps, h=h if feeds_next else None)
+        return StreamRows(h) if feeds_next else None

@@ -9,7 +9,7 @@ import torch
 
 from ..ops import kernels
 from ..registry import EMBEDDINGS, HEADS
-from .base import EMBEDDING, MATRIX, BuildEnv, Part, TensorSpec
+from .base import EMBEDDING, MATRIX, VECTOR, BuildEnv, Part, TensorSpec
 
 
 @EMBEDDINGS.register("token_embedding")
@@ -27,8 +27,37 @@ class TokenEmbedding(Part):
     def load(self, tensors, env: BuildEnv) -> None:
         self.weight = tensors["weight"].contiguous()
 
-    def forward(self, x: torch.Tensor, tokens: torch.Tensor) -> None:
+    def forward(self, x: torch.Tensor, tokens: torch.Tensor, batch=None) -> None:
         kernels.embed(x, self.weight, tokens, self.scale)
+
+
+@EMBEDDINGS.register("token_position_embedding")
+class TokenPositionEmbedding(TokenEmbedding):
+    """x = embed[token] * scale + positions[p]: a learned vector per position p (counted from 0 in each
+    sequence, not scaled) beside the token's row.  The table of `max_positions` rows is the tensor
+    `position_tensor` of the model (not under the part's prefix); the plan's `max_positions` makes the engine
+    refuse a step that would go beyond it."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, max_positions: int, position_tensor: str = "positions",
+                 scale: float = 1.0):
+        super().__init__(vocab_size, hidden_size, scale)
+        self.P = int(max_positions)
+        self.position_tensor = str(position_tensor)
+        self.positions: torch.Tensor | None = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        t = super().tensors()
+        t["positions"] = TensorSpec((self.P, self.D), VECTOR, shared_name=self.position_tensor)
+        return t
+
+    def load(self, tensors, env: BuildEnv) -> None:
+        super().load(tensors, env)
+        self.positions = tensors["positions"].to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, tokens: torch.Tensor, batch=None) -> None:
+        if batch is None:
+            raise ValueError("an embedding with learned positions needs the step's positions")
+        kernels.embed_positions(x, None, self.weight, tokens, self.positions, batch.row_pos, self.scale)
 
 
 @HEADS.register("linear_head")

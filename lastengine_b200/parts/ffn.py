@@ -37,17 +37,22 @@ _ACTIVATIONS = {"silu": kernels.SILU, "gelu_tanh": kernels.GELU_TANH, "clamped_s
 @FEED_FORWARDS.register("swiglu", "gated_dense")
 class SwiGLU(FeedForward):
     """f = W_down (act(W_gate h) * (W_up h)); act is silu (SwiGLU) unless `activation` names another
-    ("gelu_tanh": z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  `names`: the three tensors' names
-    under the part's prefix, (gate, up, down)."""
+    ("gelu_tanh": z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); "clamped_sigmoid" with `limit` and `alpha`:
+    g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)).
+    `names`: the three tensors' names under the part's prefix, (gate, up, down)."""
     split_norm = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 names: tuple[str, str, str] = ("w1.weight", "w3.weight", "w2.weight")):
+                 names: tuple[str, str, str] = ("w1.weight", "w3.weight", "w2.weight"),
+                 limit: float = 0.0, alpha: float = 1.0):
         self.D, self.F = int(hidden_size), int(intermediate_size)
-        if activation not in ("silu", "gelu_tanh"):
-            raise ValueError(f"unknown feed-forward activation '{activation}' (gelu_tanh, silu)")
+        if activation not in _ACTIVATIONS:
+            raise ValueError(f"unknown feed-forward activation '{activation}' ({', '.join(sorted(_ACTIVATIONS))})")
+        if activation == "clamped_sigmoid" and not limit > 0:
+            raise ValueError(f"the clamped activation needs a positive limit, got {limit}")
         self.activation = activation
         self.act = _ACTIVATIONS[activation]
+        self.limit, self.alpha = float(limit), float(alpha)
         self.n_gate, self.n_up, self.n_down = (str(n) for n in names)
         self.w13 = self.w2 = None
         self.fused = False
@@ -58,8 +63,9 @@ class SwiGLU(FeedForward):
                 self.n_down: TensorSpec((self.D, self.F), MATRIX)}
 
     def load(self, tensors, env: BuildEnv) -> None:
-        self.fused = (not env.is_float32) and self.F % 16 == 0 and self.D % 8 == 0
-        self.epilogue = kernels.SWIGLU | (self.act << 8)      # the gated epilogue with this part's activation
+        # the gated epilogue with this part's activation (None: the activation has no fused form)
+        self.epilogue = kernels.gated_epilogue(self.act, self.limit, self.alpha)
+        self.fused = (not env.is_float32) and self.F % 16 == 0 and self.D % 8 == 0 and self.epilogue is not None
         self.w13 = fuse_gate_up(tensors[self.n_gate], tensors[self.n_up], self.fused)
         self.w2 = tensors[self.n_down].contiguous()
 
@@ -79,7 +85,7 @@ class SwiGLU(FeedForward):
             if self.act == kernels.SILU:
                 kernels.swiglu(a, gu)
             else:
-                kernels.gated_act(a, gu, self.act)
+                kernels.gated_act(a, gu, self.act, self.limit, self.alpha)
         kernels.linear(out, a, self.w2, kernels.ACCUMULATE if accumulate else kernels.STORE,
                        emit=emit if accumulate else None)
 
@@ -93,18 +99,33 @@ class SigmoidTopKMoE(FeedForward):
     chosen (ties to the lower index) and weighted by the softmax over the chosen logits alone.
     `activation="clamped_sigmoid"` with `limit` and `alpha`: g = min(W_gate h, limit),
     u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1).
+    `router="softmax_grouped"` with `groups=(count, keep)`: scores s = softmax(Wr h) over all experts; choice
+    scores s + bias (the bias chooses, it does not weigh); the experts form `count` equal groups of neighbours,
+    a group's score is its largest choice score, and only experts of the `keep` best groups can be chosen (the
+    others' choice scores count as minus infinity); weights are the chosen s over their sum (+ 1e-20).
+    `shared_size` > 0: one more expert of that width and the same activation runs for every row and is added
+    (tensors "shared_gate"/"shared_up"/"shared_down").
     `names`: "router", "bias", and "gate"/"up"/"down" with `{e}` standing for the expert's number."""
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_size: int,
                  norm_topk: bool = True, use_bias: bool = True, scaling: float = 1.0,
                  bias_std: float = 0.1, router: str = "sigmoid", activation: str = "silu",
-                 limit: float = 0.0, alpha: float = 1.0, names: dict[str, str] | None = None):
+                 limit: float = 0.0, alpha: float = 1.0, names: dict[str, str] | None = None,
+                 groups: tuple[int, int] | None = None, shared_size: int = 0):
         if not 1 <= top_k <= min(num_experts, 16):
             raise ValueError(f"top-{top_k} of {num_experts} experts: the router takes 1..min(experts, 16)")
         if num_experts > 256:
             raise ValueError(f"{num_experts} experts: the router takes at most 256")
-        if router not in ("sigmoid", "softmax_chosen"):
-            raise ValueError(f"unknown router '{router}' (sigmoid, softmax_chosen)")
+        if router not in ("sigmoid", "softmax_chosen", "softmax_grouped"):
+            raise ValueError(f"unknown router '{router}' (sigmoid, softmax_chosen, softmax_grouped)")
+        self.groups = None
+        if router == "softmax_grouped":
+            count, keep = (int(groups[0]), int(groups[1])) if groups is not None else (1, 1)
+            if not (1 <= keep <= count <= 255 and num_experts % count == 0 and keep * (num_experts // count) >= top_k):
+                raise ValueError(f"{keep} of {count} groups over {num_experts} experts cannot give {top_k} choices")
+            self.groups = (count, keep)
+        elif groups is not None:
+            raise ValueError("groups of experts go with the softmax_grouped router")
         if activation not in _ACTIVATIONS:
             raise ValueError(f"unknown expert activation '{activation}' ({', '.join(sorted(_ACTIVATIONS))})")
         if activation == "clamped_sigmoid" and not limit > 0:
@@ -116,13 +137,20 @@ class SigmoidTopKMoE(FeedForward):
         self.limit, self.alpha = float(limit), float(alpha)
         self.n = {"router": "gate.weight", "bias": "expert_bias", "gate": "experts.{e}.w1.weight",
                   "up": "experts.{e}.w3.weight", "down": "experts.{e}.w2.weight"}
+        self.n.update({"shared_gate": "shared.gate", "shared_up": "shared.up", "shared_down": "shared.down"})
         self.n.update(names or {})
         self.router_w = self.router_b = self.w13 = self.w2 = None
         self.fused = False
+        self.shared = None
+        if shared_size:
+            self.shared = SwiGLU(hidden_size, shared_size, activation,
+                                 (self.n["shared_gate"], self.n["shared_up"], self.n["shared_down"]), limit, alpha)
 
     def tensors(self) -> dict[str, TensorSpec]:
         n = self.n
         t = {n["router"]: TensorSpec((self.E, self.D), VECTOR)}
+        if self.shared is not None:
+            t.update(self.shared.tensors())
         if self.use_bias:
             t[n["bias"]] = TensorSpec((self.E,), BIAS, std=self.bias_std)
         for e in range(self.E):
@@ -142,9 +170,12 @@ class SigmoidTopKMoE(FeedForward):
         self.w13 = torch.stack([fuse_gate_up(tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)],
                                              self.fused) for e in range(self.E)]).contiguous()
         self.w2 = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.E)]).contiguous()
+        if self.shared is not None:
+            self.shared.load(tensors, env)
 
     def flops_per_row(self) -> int:
-        return 2 * self.D * self.E + self.k * 6 * self.D * self.Fe       # the router, and k experts of three matrices
+        # the router, k experts of three matrices, and the shared expert
+        return 2 * self.D * self.E + self.k * 6 * self.D * self.Fe + (self.shared.flops_per_row() if self.shared else 0)
 
     def unread_weight_bytes(self, rows: int) -> float:
         """With uniform routing an expert is chosen by none of `rows` rows with probability (1 - k/E)^rows."""
@@ -160,7 +191,7 @@ class SigmoidTopKMoE(FeedForward):
         ids = ws.get("moe.ids", (M, self.k), torch.int32)
         wts = ws.get("moe.w", (M, self.k), torch.float32)
         kernels.moe_router(ids, wts, h, self.router_w, self.router_b, self.norm_topk, self.scaling,
-                           softmax_chosen=self.router == "softmax_chosen")
+                           softmax_chosen=self.router == "softmax_chosen", softmax_groups=self.groups)
         offsets = ws.get("moe.offsets", (self.E + 1,), torch.int32)
         sorted_pair = ws.get("moe.sorted", (P,), torch.int32)
         pair_row = ws.get("moe.rows", (P,), torch.int32)
@@ -180,3 +211,5 @@ class SigmoidTopKMoE(FeedForward):
         ys = ws.get("moe.ys", (P, self.D), torch.float32)
         kernels.linear(ys, a, self.w2, group_offsets=offsets, rows_hint=P)
         kernels.moe_combine(out, ys, pair_row, wts, accumulate)
+        if self.shared is not None:
+            self.shared.forward(h, out, True, batch, env)

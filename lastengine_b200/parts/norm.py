@@ -10,7 +10,7 @@ import torch
 
 from ..ops import kernels
 from ..registry import NORMS
-from .base import NORM, NORM_AROUND_ZERO, BuildEnv, Part, TensorSpec
+from .base import BIAS, NORM, NORM_AROUND_ZERO, BuildEnv, Part, TensorSpec
 
 
 @NORMS.register("rmsnorm")
@@ -42,24 +42,31 @@ class RMSNorm(Part):
 
 @NORMS.register("layernorm")
 class LayerNorm(Part):
-    """y = (x - mean(x)) / sqrt(var(x) + eps) * w with var the mean of the squared deviations; a weight,
-    no bias.  It takes a mean off the row, so it cannot be split between two products as the RMS norm is."""
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w (+ b) with var the mean of the squared deviations; a weight
+    and, with `bias`, an additive term under the name `bias_tensor`.  It takes a mean off the row, so it cannot
+    be split between two products as the RMS norm is."""
     splittable = False
 
-    def __init__(self, size: int, eps: float, tensor: str = "weight"):
+    def __init__(self, size: int, eps: float, tensor: str = "weight", bias: bool = False, bias_tensor: str = "bias"):
         self.size = int(size)
         self.eps = float(eps)
         self.tensor = str(tensor)
+        self.has_bias, self.bias_tensor = bool(bias), str(bias_tensor)
         self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, TensorSpec]:
-        return {self.tensor: TensorSpec((self.size,), NORM)}
+        t = {self.tensor: TensorSpec((self.size,), NORM)}
+        if self.has_bias:
+            t[self.bias_tensor] = TensorSpec((self.size,), BIAS)
+        return t
 
     def load(self, tensors: dict[str, torch.Tensor], env: BuildEnv) -> None:
         self.weight = tensors[self.tensor].to(torch.float32).contiguous()
+        self.bias = tensors[self.bias_tensor].to(torch.float32).contiguous() if self.has_bias else None
 
     def forward(self, out: torch.Tensor, x: torch.Tensor, rows: torch.Tensor | None = None,
                 add: bool = False) -> None:
         if add:
             raise NotImplementedError("a layer norm added into the residual stream")
-        kernels.layernorm(out, x, self.weight, self.eps, rows=rows)
+        kernels.layernorm(out, x, self.weight, self.eps, rows=rows, bias=self.bias)

@@ -29,7 +29,7 @@ def check_names(specs: dict[str, TensorSpec], found: dict[str, tuple[int, ...]],
     """`found`: canonical name -> shape in the file.  Raises one WeightsError listing everything."""
     missing = [n for n, s in specs.items() if n not in found and not s.optional]
     unexpected = [n for n in found if n not in specs]
-    wrong = [(n, specs[n].shape, found[n]) for n in specs if n in found and tuple(found[n]) != tuple(specs[n].shape)]
+    wrong = [(n, specs[n].shape, found[n]) for n in specs if n in found and not specs[n].fits(tuple(found[n]))]
     if not (missing or unexpected or wrong):
         return
     lines = [f"{where}: the checkpoint does not fit the model"]

@@ -30,6 +30,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, std: float, norm_init:
     dev = torch.device(device)
     g = torch.Generator(device=dev)
     g.manual_seed(_seed_for(seed, name))
+    if -1 in spec.shape:
+        spec = TensorSpec(spec.concrete_shape(), spec.role, spec.std, spec.optional, spec.shared_name)
     if spec.role == NORM:
         if norm_init == "ones":
             return torch.ones(spec.shape, dtype=torch.float32, device=dev)
