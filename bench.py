@@ -293,8 +293,9 @@ def _classes(summary: dict, work: dict, unit: str, per: float, peak: float, wher
 
 # ---- the Zekivik design beside the LFM3 hybrid at equal layer sizes (--compare zekivik) -------------------
 def zekivik_config(width: int, ff: int, heads: int, kv_heads: int, dim: int, vdim: int, ret_heads: int,
-                   ret_dim: int, ret_vdim: int, layers: int, vocab: int) -> dict:
-    """Layers alternate retention and attention, every layer with a feed-forward; the first two run twice."""
+                   ret_dim: int, ret_vdim: int, layers: int, vocab: int, loop: bool = True) -> dict:
+    """Layers alternate retention and attention, every layer with a feed-forward; the first two run twice
+    (`loop`)."""
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": 4, "scale": dim ** -0.5,
            "rot": {"dims": dim, "base": 1000000.0}}
     ret = {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim,
@@ -302,7 +303,7 @@ def zekivik_config(width: int, ff: int, heads: int, kv_heads: int, dim: int, vdi
     ls = [{"type": "retention" if i % 2 == 0 else "attention", "mixer": ret if i % 2 == 0 else att,
            "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]
     return {"architecture": "Zekivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": ls,
-            "loop": {"start": 0, "stop": 2, "times": 2}}
+            "loop": {"start": 0, "stop": 2, "times": 2 if loop else 1}}
 
 
 def lfm3_like(width: int, ff: int, heads: int, kv_heads: int, dim: int, runs: int, vocab: int) -> dict:
@@ -402,6 +403,74 @@ def _lenesun_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict
     return {"bytes": out, "attention_flops": attn_flops}
 
 
+# ---- the Kisilix design beside the Zekivik hybrid at equal layer sizes (--compare kisilix) ---------------
+def kisilix_config(width: int, ff: int, heads: int, kv_heads: int, dim: int, vdim: int, ret_heads: int, ret_dim: int,
+                   ret_vdim: int, layers: int, vocab: int, window: int, pool: int) -> dict:
+    """Recurrent layers (the delta rule and the state-space layer in turn) alternate with windowed attention;
+    every layer has the dense feed-forward.  The recurrent layers take the sizes the other design's retention
+    has (key size = rows of a head's state), the attention its head sizes."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+           "rot": {"dims": dim, "base": 1000000.0}, "mask": {"size": window, "pool": pool}}
+    dlt = {"heads": ret_heads, "kv_heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim, "conv": 4}
+    ssm = {"heads": ret_heads, "vdim": ret_vdim, "state": ret_dim, "groups": 1, "norm_groups": 1, "conv": 4}
+    ls = []
+    for i in range(layers):
+        kind, mixer = ("attention", att) if i % 2 else (("channel_delta", dlt) if i % 4 == 0 else ("mamba2", ssm))
+        ls.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}})
+    return {"architecture": "Kisilix", "vocab": vocab, "width": width, "max_positions": 4096, "norm": {"eps": 1e-5},
+            "postln_alpha": 1.0, "layers": ls}
+
+
+KISILIX_SIZES = {   # as COMPARE_SIZES, and the attention's window and pooled block
+    "w2048": dict(COMPARE_SIZES["w2048"], window=1024, pool=64),
+    "w1024": dict(COMPARE_SIZES["w1024"], window=512, pool=16),
+    "w2048-v32": dict(COMPARE_SIZES["w2048-v32"], window=1024, pool=64),
+}
+
+
+def _seen_keys(i: int, window: int, pool: int) -> int:
+    """Positions and pooled blocks that position i sees."""
+    return min(i + 1, window) + (max(0, i - window + 1) // pool if pool else 0)
+
+
+def _kisilix_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict:
+    """What a step's launches of the design's own kernels have to move (bytes) or compute (flops), by entry point.
+    `rows` rows in all, of `batch` sequences that end at `context`."""
+    W = cfg["width"]
+    by = {"leb_postnorm_residual": 0, "leb_gated_act": 0, "leb_causal_conv": 0, "leb_delta_prep": 0, "leb_ssm_prep": 0,
+          "leb_gated_recurrence": 0, "leb_group_norm_gate": 0, "leb_pooled_attn_prep": 0, "leb_attention_pooled": 0}
+    fl = {"leb_gated_recurrence": 0, "leb_attention_pooled": 0}
+    per_seq = rows // batch
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        n_sub = 2 if l["mlp"] else 1
+        by["leb_postnorm_residual"] += n_sub * rows * W * (4 + 4 + 4 + 2)            # x and y read (float), x and its bfloat16 copy written
+        if l["mlp"]:
+            by["leb_gated_act"] += rows * l["mlp"]["ff"] * (8 + 2)
+        if l["type"] == "attention":
+            nh, nkv, hd, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            by["leb_pooled_attn_prep"] += rows * ((nh + nkv) * hd + nkv * vd) * (4 + 2)
+            win, pool = m["mask"]["size"], m["mask"]["pool"]
+            seen = sum(_seen_keys(i, win, pool) for i in range(context - per_seq, context))
+            fl["leb_attention_pooled"] += 2 * nh * (hd + vd) * seen * batch
+            by["leb_attention_pooled"] += batch * _seen_keys(context - 1, win, pool) * nkv * (hd + vd) * 2 + rows * nh * (hd + vd) * 2
+        else:
+            delta = l["type"] == "channel_delta"
+            H, e = m["heads"], m["vdim"]
+            d = m["dim"] if delta else m["state"]
+            kq = 2 * (m["kv_heads"] if delta else m["groups"]) * d
+            C = kq + H * e
+            by["leb_causal_conv"] += rows * C * 8 + batch * C * (m["conv"] - 1) * 8
+            if delta:
+                by["leb_delta_prep"] += rows * (2 * C + 2 * H * d + 2 * H) * 4
+            else:
+                by["leb_ssm_prep"] += rows * (2 * C + 3 * H) * 4
+            by["leb_gated_recurrence"] += rows * (kq + 2 * H * e + (H * d if delta else H) + H) * 4 + batch * H * d * e * 8
+            fl["leb_gated_recurrence"] += rows * H * d * e * (8 if delta else 6)
+            by["leb_group_norm_gate"] += rows * H * e * (4 + 4 + 2)
+    return {"bytes": by, "flops": fl}
+
+
 def compare_designs(which: str, steps: int, warmup: int) -> int:
     import numpy as np
     import torch
@@ -410,8 +479,12 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
     results = {}
-    for size_name, sz in (COMPARE_SIZES if which == "zekivik" else LENESUN_SIZES).items():
-        if which == "zekivik":
+    other = "zekivik" if which == "kisilix" else "lfm3"
+    for size_name, sz in {"zekivik": COMPARE_SIZES, "lenesun": LENESUN_SIZES, "kisilix": KISILIX_SIZES}[which].items():
+        if which == "kisilix":
+            zc = kisilix_config(vocab=32768, **sz)
+            lc = zekivik_config(vocab=32768, loop=False, **{k: v for k, v in sz.items() if k not in ("window", "pool")})
+        elif which == "zekivik":
             zc = zekivik_config(vocab=32768, **sz)
             runs = sz["layers"] + 2
             lc = lfm3_like(sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["dim"], runs, 32768)
@@ -419,15 +492,21 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             zc = lenesun_config(vocab=32768, **sz)
             lc = lfm3_moe_like(sz["width"], sz["heads"], sz["dim"], sz["experts"], sz["top"], sz["ff"], sz["layers"], 32768)
         row = {}
-        for label, cfg in ((which, zc), ("lfm3", lc)):
+        for label, cfg in ((which, zc), (other, lc)):
             eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 2304 + 4096, max_seqs=16)
             nums = model_numbers(eng)
             r = {"weights_gb": round(nums["weight_bytes"] / 1e9, 3)}
             print(f"[bench] {size_name} {label}: {r['weights_gb']} GB of weights", file=sys.stderr, flush=True)
             pre_ms = time_prefill(eng, PREFILL_TOKENS, 3, 5, rng)
             print(f"[bench] {size_name} {label}: prompt of {PREFILL_TOKENS} tokens {pre_ms:.3f} ms", file=sys.stderr, flush=True)
-            flops = (PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"]
-                     + nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
+            if label == "kisilix":      # a position sees its window and the pooled blocks behind it, not every earlier one
+                attn_flops = _kisilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS)["flops"]["leb_attention_pooled"]
+                kv_seen = [sum(_seen_keys(2047, l["mixer"]["mask"]["size"], l["mixer"]["mask"]["pool"]) * l["mixer"]["kv_heads"]
+                               * (l["mixer"]["dim"] + l["mixer"]["vdim"]) * 2 for l in cfg["layers"] if l["type"] == "attention")]
+            else:
+                attn_flops = nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2
+                kv_seen = None
+            flops = PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"] + attn_flops
             r["prefill_2048_ms"] = pre_ms
             r["prefill_tok_s"] = PREFILL_TOKENS / (pre_ms / 1e3)
             r["prefill_frac_of_bf16_peak"] = flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
@@ -436,7 +515,9 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
                 r[f"decode_b{b}_ms"] = d["ms_per_step"]
                 r[f"decode_b{b}_tok_s"] = d["tok_s"]
                 r[f"decode_b{b}_launches"] = d["launches_per_step"]
-                r[f"decode_b{b}_frac_of_hbm"] = decode_step_bytes(eng, nums, b, d["avg_context"]) / (d["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+                step_bytes = decode_step_bytes(eng, nums, b, d["avg_context"]) if kv_seen is None else \
+                    eng.weight_bytes_read(b) + b * kv_seen[0] + 2 * b * nums["state_bytes_per_seq"]
+                r[f"decode_b{b}_frac_of_hbm"] = step_bytes / (d["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
                 print(f"[bench] {size_name} {label}: decode b{b} {d['ms_per_step']:.4f} ms/step", file=sys.stderr, flush=True)
             # every entry point of a prompt and of a decode step, one after the other under the event timer
             toks = rng.integers(0, eng.vocab_size, size=PREFILL_TOKENS).tolist()
@@ -457,8 +538,19 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             eng.release(seqs)
             dec_k = t.summary()
             by, fl = {}, {}
-            if label == "zekivik":
-                by = {"prefill": _new_kernel_bytes(zc, PREFILL_TOKENS, 1), "decode_b8": _new_kernel_bytes(zc, 8, 8)}
+            if label == "kisilix":
+                wp, wd = _kisilix_kernel_work(zc, PREFILL_TOKENS, 1, PREFILL_TOKENS), _kisilix_kernel_work(zc, 8, 8, 2048)
+                by = {"prefill": wp["bytes"], "decode_b8": wd["bytes"]}
+                fl = {"prefill": wp["flops"]}
+            elif label == "zekivik":
+                by = {"prefill": _new_kernel_bytes(cfg, PREFILL_TOKENS, 1), "decode_b8": _new_kernel_bytes(cfg, 8, 8)}
+                if which == "kisilix":     # the like kernels of the other side: retention's flops, attention's flops and cache bytes
+                    ret = sum(6 * l["mixer"]["heads"] * l["mixer"]["dim"] * l["mixer"]["vdim"] for l in cfg["layers"] if l["type"] == "retention")
+                    att = nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2
+                    fl = {"prefill": {"leb_retention": ret * PREFILL_TOKENS, "leb_attention_prefill_tc": att,
+                                      "leb_attention_prefill": att, "leb_attention_general": att}}
+                    for name in ("leb_attention_decode", "leb_attention_decode_prep", "leb_attention_general"):
+                        by["decode_b8"][name] = 8 * 2048 * nums["kv_bytes_per_token"]
             elif label == "lenesun":
                 wp, wd = _lenesun_kernel_work(zc, PREFILL_TOKENS, 1, PREFILL_TOKENS), _lenesun_kernel_work(zc, 8, 8, 2048)
                 by = {"prefill": {k: v for k, v in wp["bytes"].items() if k != "leb_latent_attention"}, "decode_b8": wd["bytes"]}
@@ -486,8 +578,9 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             del eng
             torch.cuda.empty_cache()
         results[size_name] = {"sizes": sz, **row}
-    print(json.dumps({"compare": which, "against": "lfm3 hybrid at equal layer sizes" if which == "zekivik" else
-                      "lfm3 with attention and experts in every layer at equal layer sizes", "dtype": "bf16",
+    against = {"zekivik": "lfm3 hybrid at equal layer sizes", "kisilix": "zekivik hybrid at equal layer sizes",
+               "lenesun": "lfm3 with attention and experts in every layer at equal layer sizes"}[which]
+    print(json.dumps({"compare": which, "against": against, "dtype": "bf16",
                       "data": "synthetic (random weights, uniform random token ids)", "peaks": pk_src,
                       "prefill_tokens": PREFILL_TOKENS, "decode_context": 2048, "steps": steps, "warmup": warmup,
                       "sizes": results}))
@@ -512,9 +605,9 @@ def main() -> int:
     ap.add_argument("--unequal", type=int, default=0, metavar="N",
                     help="instead of the default run: N requests with prompts of U[64, 2048] tokens generate "
                          "--steps tokens each in one batch through the Python entry point (prints its own JSON line)")
-    ap.add_argument("--compare", default="", choices=["", "zekivik", "lenesun"],
+    ap.add_argument("--compare", default="", choices=["", "zekivik", "lenesun", "kisilix"],
                     help="instead of the default run: prefill and decode of that design at a few layer sizes beside "
-                         "the LFM3 hybrid at equal sizes, with every kernel's time (prints its own JSON line)")
+                         "the closest other design at equal sizes, with every kernel's time (prints its own JSON line)")
     args = ap.parse_args()
 
     if args.compare:

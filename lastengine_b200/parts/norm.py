@@ -58,7 +58,7 @@ class LayerNorm(Part):
     def tensors(self) -> dict[str, TensorSpec]:
         t = {self.tensor: TensorSpec((self.size,), NORM)}
         if self.has_bias:
-            t[self.bias_tensor] = TensorSpec((self.size,), BIAS)
+            t[self.bias_tensor] = TensorSpec((self.size,), BIAS, std=0.1)
         return t
 
     def load(self, tensors: dict[str, torch.Tensor], env: BuildEnv) -> None:
