@@ -67,14 +67,29 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int GS>   // query heads per kv head (1, 2, 4, 8): a tile is GS heads x 128/GS positions
+// Pooled blocks behind the window (POOLED): the first `window`-less part of a row's keys is one pooled key and
+// value per complete block of `pool` positions, held in pools of the same layout with a page list of their own
+// (row b of a pooled page list is block b).  A tile walks the pooled pages that its last row sees, then the
+// window's pages; row i sees the first max(0, i - window + 1) / pool blocks.  With POOLED the weights go to the
+// second product as two bfloat16 terms, p = hi + lo (16 significant bits instead of 8; the row sum uses the
+// float p), written over the scores they came from: the product of page i+2's scores, which overwrites them, is
+// issued after the products that read them, and the tensor pipe runs its products in the order of issue.
+__device__ __forceinline__ int atc_blocks_seen(int qpos, int window, int pool) {
+  const int past = qpos - window + 1;
+  return (window > 0 && pool > 0 && past > 0) ? past / pool : 0;
+}
+
+template <int GS, bool POOLED>   // GS query heads per kv head (1, 2, 4, 8): a tile is GS heads x 128/GS positions
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
-                            const int* __restrict__ block_table, int bt_width, const int* __restrict__ seq_slot,
+                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_pk,
+                            const __grid_constant__ CUtensorMap map_pv, bf16* __restrict__ out,
+                            const int* __restrict__ block_table, int bt_width, const int* __restrict__ pool_table,
+                            int pt_width, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_pos0, const int* __restrict__ seq_qstart,
                             const int* __restrict__ seq_qlen, const bf16* __restrict__ gate, int gate_stride,
-                            int nh, int nkv, int window, float scale, int* __restrict__ status) {
+                            int nh, int nkv, int window, int pool, float scale, const float* __restrict__ head_scale,
+                            const float* __restrict__ freq_v, int* __restrict__ status) {
   constexpr int HD = 64, PAGE = 64, TP = 128 / GS, NS = ATC_STAGES;
   constexpr int Q_BYTES = 128 * HD * 2, KV_BYTES = PAGE * HD * 2;
   extern __shared__ uint8_t atc_raw[];
@@ -115,6 +130,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int key_lo_tile = window > 0 ? max(0, q_lo - window + 1) : 0;
   const int jb0 = key_lo_tile / PAGE, nblk = (key_hi - 1) / PAGE - jb0 + 1;
   const int* table = block_table + (size_t)b * bt_width;
+  const int nb_tile = POOLED ? atc_blocks_seen(key_hi - 1, window, pool) : 0;   // pooled blocks the tile's last row sees
+  const int npp = (nb_tile + PAGE - 1) / PAGE;                                  // pages of them, walked first
+  const int n_it = npp + nblk;
+  const int* ptable = POOLED ? pool_table + (size_t)b * pt_width : table;
 
   if (threadIdx.x == 0) {
     abort_s = 0;
@@ -151,18 +170,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_expect_tx(&q_full, Q_BYTES);
       for (int g = 0; g < GS; g++)
         tma_load_2d(sq + g * (TP * HD * 2), &map_q, &q_full, (h0 + g) * HD, (int)m_base);
-      int next_page = table[jb0];
-      for (int i = 0; i < nblk && ok; i++) {
+      auto page_of = [&](int i) { return (POOLED && i < npp) ? ptable[i] : table[jb0 + i - npp]; };
+      int next_page = page_of(0);
+      for (int i = 0; i < n_it && ok; i++) {
         const int s = i % NS;
         int page = next_page;
-        if (i + 1 < nblk) next_page = table[jb0 + i + 1];   // asked for before the wait below
+        if (i + 1 < n_it) next_page = page_of(i + 1);   // asked for before the wait below
         if (!mbar_wait(&kv_empty[s], ((i / NS) & 1) ^ 1, abort_flag)) { atomicExch(status, 11); ok = false; break; }
         if (page < 0) page = 0;   // a page the window has left behind: every key of it is masked
         const int y = (page * nkv + kvh) * PAGE;
+        const bool pooled = POOLED && i < npp;
         mbar_expect_tx(&k_full[s], KV_BYTES);
-        tma_load_2d(sk + s * KV_BYTES, &map_k, &k_full[s], 0, y);
+        tma_load_2d(sk + s * KV_BYTES, pooled ? &map_pk : &map_k, &k_full[s], 0, y);
         mbar_expect_tx(&v_full[s], KV_BYTES);
-        tma_load_2d(sv + s * KV_BYTES, &map_v, &v_full[s], 0, y);
+        tma_load_2d(sv + s * KV_BYTES, pooled ? &map_pv : &map_v, &v_full[s], 0, y);
       }
     }
   } else if (warp == 5) {
@@ -181,16 +202,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       };
       if (!mbar_wait(&q_full, 0, abort_flag)) { atomicExch(status, 13); ok = false; }
       if (ok) ok = scores(0);
-      for (int i = 0; i < nblk && ok; i++) {
-        if (i + 1 < nblk && !scores(i + 1)) { ok = false; break; }
+      for (int i = 0; i < n_it && ok; i++) {
+        if (i + 1 < n_it && !scores(i + 1)) { ok = false; break; }
         const int s = i % NS;
         if (!mbar_wait(&p_full[i & 1], (i >> 1) & 1, abort_flag)) { atomicExch(status, 14); ok = false; break; }
         if (!mbar_wait(&v_full[s], (i / NS) & 1, abort_flag)) { atomicExch(status, 15); ok = false; break; }
         tc_fence_after();
         const uint32_t va = smem_u32(sv + s * KV_BYTES);
+        if (POOLED) {
+          const uint32_t t_p = t_s0 + 64 * (i & 1);   // hi in the scores' first 32 columns, lo in the next 32
 #pragma unroll
-        for (int kk = 0; kk < PAGE / 16; kk++)
-          umma_bf16_ts(t_o, t_p0 + 32 * (i & 1) + kk * 8, make_desc(va + kk * 32), IDESC, (i > 0 || kk > 0));
+          for (int kk = 0; kk < PAGE / 16; kk++)
+            umma_bf16_ts(t_o, t_p + kk * 8, make_desc(va + kk * 32), IDESC, (i > 0 || kk > 0));
+#pragma unroll
+          for (int kk = 0; kk < PAGE / 16; kk++)
+            umma_bf16_ts(t_o, t_p + 32 + kk * 8, make_desc(va + kk * 32), IDESC, 1);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < PAGE / 16; kk++)
+            umma_bf16_ts(t_o, t_p0 + 32 * (i & 1) + kk * 8, make_desc(va + kk * 32), IDESC, (i > 0 || kk > 0));
+        }
         umma_commit(&kv_empty[s]);
         umma_commit(&pv_done[i & 1]);
       }
@@ -202,10 +233,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int qpos = q_lo + pi;
     const int key_lo_row = window > 0 ? max(0, qpos - window + 1) : 0;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const float scale2 = scale * 1.4426950408889634f;
+    const float scale2 = (head_scale ? head_scale[h0 + g] : scale) * 1.4426950408889634f;
+    const int nb_row = POOLED ? atc_blocks_seen(qpos, window, pool) : 0;
     float m_used = ATC_NEG, l = 0.f;
-    for (int i = 0; i < nblk && ok; i++) {
-      const int key0 = (jb0 + i) * PAGE, bsel = i & 1, s = i % NS;
+    for (int i = 0; i < n_it && ok; i++) {
+      const bool pooled = POOLED && i < npp;
+      const int key0 = pooled ? i * PAGE : (jb0 + i - npp) * PAGE, bsel = i & 1, s = i % NS;
       if (!mbar_wait(&s_full[bsel], (i >> 1) & 1, abort_flag)) { atomicExch(status, 16); ok = false; break; }
       tc_fence_after();
       uint32_t v[64];
@@ -213,7 +246,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tmem_ld32(t_s0 + 64 * bsel + lane_base + 32, v + 32);
       tmem_ld_wait();
       // columns [c_lo, c_hi] of this page are keys this row may see
-      const int c_lo = max(0, key_lo_row - key0), c_hi = row_valid ? min(PAGE - 1, qpos - key0) : -1;
+      const int c_lo = pooled ? 0 : max(0, key_lo_row - key0);
+      const int c_hi = row_valid ? min(PAGE - 1, (pooled ? nb_row - 1 : qpos) - key0) : -1;
       // The scores stay as the product left them; the scale goes into the exponent's multiply-add.
       float rm[4] = {ATC_NEG, ATC_NEG, ATC_NEG, ATC_NEG};   // four chains instead of one of 64 steps
       if (c_lo == 0 && c_hi == PAGE - 1) {
@@ -252,7 +286,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (move) m_used = m_new;
       }
       const float m_ref = m_used > 0.5f * ATC_NEG ? m_used : 0.f;
-      uint32_t pk[32];
+      uint32_t pk[32], pl[POOLED ? 32 : 1];
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < PAGE; c += 2) {
@@ -261,17 +295,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ps[(c >> 1) & 3] += p0 + p1;
         __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+        if (POOLED) {
+          __nv_bfloat162 pr = __floats2bfloat162_rn(p0 - __bfloat162float(pp.x), p1 - __bfloat162float(pp.y));
+          pl[c >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+        }
       }
       l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
       // P[bsel] was last read by the product of page i-2
       if (i >= 2 && !mbar_wait(&pv_done[bsel], ((i - 2) >> 1) & 1, abort_flag)) { atomicExch(status, 18); ok = false; break; }
       tc_fence_after();
-      tmem_st32(t_p0 + 32 * bsel + lane_base, pk);
+      if (POOLED) {
+        tmem_st32(t_s0 + 64 * bsel + lane_base, pk);
+        tmem_st32(t_s0 + 64 * bsel + 32 + lane_base, pl);
+      } else {
+        tmem_st32(t_p0 + 32 * bsel + lane_base, pk);
+      }
       tmem_st_wait();
-      if (key0 + PAGE > key_hi) {
-        // the page with the end of the sequence: its value columns beyond the end become zero
+      const int key_end = pooled ? nb_tile : key_hi;
+      if (key0 + PAGE > key_end) {
+        // the page with the end of the sequence (or of the pooled blocks): its value columns beyond it become zero
         if (!mbar_wait(&v_full[s], (i / NS) & 1, abort_flag)) { atomicExch(status, 19); ok = false; break; }
-        const int n_valid = key_hi - key0;
+        const int n_valid = key_end - key0;
         if (r < HD) {
           uint8_t* vrow = sv + s * KV_BYTES + r * 128;   // dimension r: 64 positions, 16-byte pieces swizzled by r & 7
           for (int cc = n_valid / 8; cc < 8; cc++) {
@@ -286,30 +330,42 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (lane == 0) mbar_arrive(&p_full[bsel]);   // one arrival per softmax warp
     }
     if (ok) {
-      if (!mbar_wait(&pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag)) { atomicExch(status, 20); ok = false; }
+      if (!mbar_wait(&pv_done[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag)) { atomicExch(status, 20); ok = false; }
     }
     if (ok) {
       tc_fence_after();
       float inv = l > 0.f ? 1.0f / l : 0.f;
       if (gate && row_valid) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(m_base + pi) * gate_stride + h0 + g])));
       uint4* orow = reinterpret_cast<uint4*>(out + ((m_base + pi) * nh + h0 + g) * HD);
+      uint32_t o[HD];
+      tmem_ld32(t_o + lane_base, o);
+      tmem_ld32(t_o + lane_base + 32, o + 32);
+      tmem_ld_wait();
+      if (row_valid) {
 #pragma unroll
-      for (int hcol = 0; hcol < HD; hcol += 32) {
-        uint32_t o[32];
-        tmem_ld32(t_o + lane_base + hcol, o);
-        tmem_ld_wait();
-        if (row_valid) {
+        for (int c = 0; c < HD; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * inv);
+        if (POOLED && freq_v) {
+          // values were cached turned by their positions: the sum is turned back by the query's (pairs c, c + 32)
+          const float fpos = (float)qpos;
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint4 w;
-            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              __nv_bfloat162 pp = __floats2bfloat162_rn(__uint_as_float(o[c + 2 * e]) * inv, __uint_as_float(o[c + 2 * e + 1]) * inv);
-              wp[e] = *reinterpret_cast<uint32_t*>(&pp);
-            }
-            orow[(hcol + c) / 8] = w;
+          for (int c = 0; c < HD / 2; c++) {
+            float sn, cs;
+            sincosf(fpos * freq_v[c], &sn, &cs);
+            const float a = __uint_as_float(o[c]), bb = __uint_as_float(o[c + HD / 2]);
+            o[c] = __float_as_uint(a * cs + bb * sn);
+            o[c + HD / 2] = __float_as_uint(bb * cs - a * sn);
           }
+        }
+#pragma unroll
+        for (int c = 0; c < HD; c += 8) {
+          uint4 w;
+          uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            __nv_bfloat162 pp = __floats2bfloat162_rn(__uint_as_float(o[c + 2 * e]), __uint_as_float(o[c + 2 * e + 1]));
+            wp[e] = *reinterpret_cast<uint32_t*>(&pp);
+          }
+          orow[c / 8] = w;
         }
       }
     }
@@ -325,6 +381,61 @@ LEB_API int leb_attention_prefill_tc_supported(int nh, int nkv, int hd, int page
   return G == 1 || G == 2 || G == 4 || G == 8;
 }
 
+template <bool POOLED>
+static int launch_attention_prefill_tc(const char* who, void* out, const void* q, int q_stride, int M, const void* k_pool,
+                                       const void* v_pool, int n_pages, const int* block_table, int bt_width,
+                                       const void* pk_pool, const void* pv_pool, int n_pooled_pages, const int* pool_table,
+                                       int pt_width, const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
+                                       const int* seq_qlen, const void* gate, int gate_stride, int B, int nh, int nkv,
+                                       int hd, int page_size, int window, int pool, float scale, const float* head_scale,
+                                       const float* freq_v, int max_qlen, int* status, cudaStream_t st) {
+  if (B <= 0 || max_qlen <= 0 || M <= 0) return 0;
+  LEB_REQUIRE(leb_attention_prefill_tc_supported(nh, nkv, hd, page_size),
+              "%s: sizes not taken (heads %d, kv heads %d, head_dim %d, page %d)", who, nh, nkv, hd, page_size);
+  LEB_REQUIRE(status != nullptr, "%s: a status word is required", who);
+  LEB_REQUIRE(((uintptr_t)q & 15) == 0 && q_stride % 8 == 0 && ((uintptr_t)out & 15) == 0,
+              "%s: q and out must be 16-byte aligned, q's row stride a multiple of 8", who);
+  const bool pooled = POOLED && pool > 0;
+  LEB_REQUIRE(!pooled || (window > 0 && pk_pool && pv_pool && pool_table && n_pooled_pages > 0),
+              "%s: pooled blocks need a window, their pools and their page lists", who);
+  const int G = nh / nkv, TP = 128 / G;
+  CUtensorMap mq, mk, mv, mpk, mpv;
+  if (tensor_map(&mq, q, M, nh * hd, q_stride, TP)) return 1;
+  if (tensor_map(&mk, k_pool, n_pages * nkv * page_size, hd, hd, page_size)) return 1;
+  if (tensor_map(&mv, v_pool, n_pages * nkv * hd, page_size, page_size, hd)) return 1;
+  if (pooled) {
+    if (tensor_map(&mpk, pk_pool, n_pooled_pages * nkv * page_size, hd, hd, page_size)) return 1;
+    if (tensor_map(&mpv, pv_pool, n_pooled_pages * nkv * hd, page_size, page_size, hd)) return 1;
+  } else {
+    mpk = mk;
+    mpv = mv;
+  }
+  dim3 grid(nkv, ceil_div(max_qlen, TP), B);
+  LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "%s: grid too large", who);
+  const size_t smem = 1024 + 128 * 64 * 2 + 2 * ATC_STAGES * 64 * 64 * 2;
+#define LEB_ATC(GS_)                                                                                              \
+  {                                                                                                               \
+    static bool set = false;                                                                                      \
+    if (!set) {                                                                                                   \
+      if (cudaFuncSetAttribute(attention_prefill_tc_kernel<GS_, POOLED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        return leb_fail("%s: %zu bytes of shared memory per block refused", who, smem);                         \
+      set = true;                                                                                                 \
+    }                                                                                                             \
+    leb_launch(attention_prefill_tc_kernel<GS_, POOLED>, grid, dim3(ATC_THREADS), smem, st,                       \
+        mq, mk, mv, mpk, mpv, (bf16*)out, block_table, bt_width, pool_table, pt_width, seq_slot, seq_pos0, seq_qstart, \
+        seq_qlen, (const bf16*)gate, gate_stride, nh, nkv, window, pooled ? pool : 0, scale, head_scale, freq_v, status); \
+  }
+  switch (G) {
+    case 1: LEB_ATC(1); break;
+    case 2: LEB_ATC(2); break;
+    case 4: LEB_ATC(4); break;
+    default: LEB_ATC(8); break;
+  }
+#undef LEB_ATC
+  LEB_CHECK_LAUNCH(who);
+  return 0;
+}
+
 // Prompt attention of the step's rows over the paged cache (which already holds their keys and
 // values).  q: [M, nh*64] with row stride q_stride; k_pool [n_pages][nkv][64][64], v_pool
 // [n_pages][nkv][64 dims][64 positions]; out [M, nh*64].  status: device int, set non-zero by a
@@ -335,39 +446,24 @@ LEB_API int leb_attention_prefill_tc(void* out, const void* q, int q_stride, int
                                      const int* seq_qlen, const void* gate, int gate_stride, int B, int nh, int nkv,
                                      int hd, int page_size, int window, float scale, int max_qlen, int* status,
                                      cudaStream_t st) {
-  if (B <= 0 || max_qlen <= 0 || M <= 0) return 0;
-  LEB_REQUIRE(leb_attention_prefill_tc_supported(nh, nkv, hd, page_size),
-              "leb_attention_prefill_tc: sizes not taken (heads %d, kv heads %d, head_dim %d, page %d)", nh, nkv, hd, page_size);
-  LEB_REQUIRE(status != nullptr, "leb_attention_prefill_tc: a status word is required");
-  LEB_REQUIRE(((uintptr_t)q & 15) == 0 && q_stride % 8 == 0 && ((uintptr_t)out & 15) == 0,
-              "leb_attention_prefill_tc: q and out must be 16-byte aligned, q's row stride a multiple of 8");
-  const int G = nh / nkv, TP = 128 / G;
-  CUtensorMap mq, mk, mv;
-  if (tensor_map(&mq, q, M, nh * hd, q_stride, TP)) return 1;
-  if (tensor_map(&mk, k_pool, n_pages * nkv * page_size, hd, hd, page_size)) return 1;
-  if (tensor_map(&mv, v_pool, n_pages * nkv * hd, page_size, page_size, hd)) return 1;
-  dim3 grid(nkv, ceil_div(max_qlen, TP), B);
-  LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention_prefill_tc: grid too large");
-  const size_t smem = 1024 + 128 * 64 * 2 + 2 * ATC_STAGES * 64 * 64 * 2;
-#define LEB_ATC(GS_)                                                                                              \
-  {                                                                                                               \
-    static bool set = false;                                                                                      \
-    if (!set) {                                                                                                   \
-      if (cudaFuncSetAttribute(attention_prefill_tc_kernel<GS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
-        return leb_fail("leb_attention_prefill_tc: %zu bytes of shared memory per block refused", smem);        \
-      set = true;                                                                                                 \
-    }                                                                                                             \
-    leb_launch(attention_prefill_tc_kernel<GS_>, grid, dim3(ATC_THREADS), smem, st,                               \
-        mq, mk, mv, (bf16*)out, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen, (const bf16*)gate, \
-        gate_stride, nh, nkv, window, scale, status);                                                             \
-  }
-  switch (G) {
-    case 1: LEB_ATC(1); break;
-    case 2: LEB_ATC(2); break;
-    case 4: LEB_ATC(4); break;
-    default: LEB_ATC(8); break;
-  }
-#undef LEB_ATC
-  LEB_CHECK_LAUNCH("leb_attention_prefill_tc");
-  return 0;
+  return launch_attention_prefill_tc<false>("leb_attention_prefill_tc", out, q, q_stride, M, k_pool, v_pool, n_pages,
+                                            block_table, bt_width, nullptr, nullptr, 0, nullptr, 0, seq_slot, seq_pos0,
+                                            seq_qstart, seq_qlen, gate, gate_stride, B, nh, nkv, hd, page_size, window, 0,
+                                            scale, nullptr, nullptr, max_qlen, status, st);
+}
+
+// The same over a window with pooled blocks behind it (pool 0: none): pk_pool / pv_pool hold one row per
+// complete block in the layout of k_pool / v_pool, pool_table [B][pt_width] their page lists; scores times
+// head_scale[h]; freq_v [32] or null: the result of a row is turned back by its position (pairs c, c + 32).
+LEB_API int leb_attention_pooled_tc(void* out, const void* q, int q_stride, int M, const void* k_pool, const void* v_pool,
+                                    int n_pages, const int* block_table, int bt_width, const void* pk_pool,
+                                    const void* pv_pool, int n_pooled_pages, const int* pool_table, int pt_width,
+                                    const int* seq_slot, const int* seq_pos0, const int* seq_qstart, const int* seq_qlen,
+                                    const float* head_scale, const float* freq_v, int B, int nh, int nkv, int hd,
+                                    int page_size, int window, int pool, int max_qlen, int* status, cudaStream_t st) {
+  LEB_REQUIRE(head_scale != nullptr, "leb_attention_pooled_tc: a factor per head is required");
+  return launch_attention_prefill_tc<true>("leb_attention_pooled_tc", out, q, q_stride, M, k_pool, v_pool, n_pages,
+                                           block_table, bt_width, pk_pool, pv_pool, n_pooled_pages, pool_table, pt_width,
+                                           seq_slot, seq_pos0, seq_qstart, seq_qlen, nullptr, 0, B, nh, nkv, hd, page_size,
+                                           window, pool, 1.0f, head_scale, freq_v, max_qlen, status, st);
 }
