@@ -45,7 +45,9 @@ pooled_prep_kernel(T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict_
   const int page = slot >= 0 ? block_table[(size_t)b * bt_width + pos / page_size] : -1;
   const int in_page = pos % page_size;
   const float fpos = (float)pos;
-  for (int hh = warp; hh < nh + 2 * nkv; hh += PAT_WARPS) {
+  {      // a warp a head: blockIdx.y counts blocks of PAT_WARPS heads of q | k | v
+    const int hh = blockIdx.y * PAT_WARPS + warp;
+    if (hh >= nh + 2 * nkv) return;
     const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
     const int width = (is_q || is_k) ? hd : vd;
     const int col = is_q ? hh * hd : (is_k ? nh * hd + (hh - nh) * hd : (nh + nkv) * hd + (hh - nh - nkv) * vd);
@@ -100,13 +102,15 @@ LEB_API int leb_pooled_attn_prep(void* q_out, void* k_pool, void* v_pool, int dt
   LEB_REQUIRE(hd >= 1 && hd <= 256 && vd >= 1 && vd <= 256, "leb_pooled_attn_prep: head sizes %d / %d outside 1..256", hd, vd);
   LEB_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0 && vd % 2 == 0, "leb_pooled_attn_prep: rotated widths must be even (%d, %d)", rot, vd);
   const size_t smem = (size_t)PAT_WARPS * (hd > vd ? hd : vd) * sizeof(float);
+  const dim3 grid(M, ceil_div(nh + 2 * nkv, PAT_WARPS));
+  LEB_REQUIRE(grid.y <= 65535, "leb_pooled_attn_prep: %d heads in a row", nh + 2 * nkv);
   LebPlainLaunches plain(true);
   if (dtype == LEB_F32)
-    leb_launch(pooled_prep_kernel<float>, dim3(M), dim3(32 * PAT_WARPS), smem, st, (float*)q_out, (float*)k_pool, (float*)v_pool,
+    leb_launch(pooled_prep_kernel<float>, grid, dim3(32 * PAT_WARPS), smem, st, (float*)q_out, (float*)k_pool, (float*)v_pool,
                proj, ldp, bias, qw, kw, eps, freq_qk, rot, freq_v, block_table, bt_width, row_seq, row_pos, seq_slot, nh, nkv,
                hd, vd, page_size);
   else if (dtype == LEB_BF16)
-    leb_launch(pooled_prep_kernel<bf16>, dim3(M), dim3(32 * PAT_WARPS), smem, st, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool,
+    leb_launch(pooled_prep_kernel<bf16>, grid, dim3(32 * PAT_WARPS), smem, st, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool,
                proj, ldp, bias, qw, kw, eps, freq_qk, rot, freq_v, block_table, bt_width, row_seq, row_pos, seq_slot, nh, nkv,
                hd, vd, page_size);
   else
@@ -137,13 +141,19 @@ pool_blocks_kernel(T* __restrict__ pk_pool, T* __restrict__ pv_pool, const T* __
   const float inv = 1.0f / (float)pool;
   for (int i = threadIdx.x; i < hd + vd; i += blockDim.x) {
     float s = 0.f;
-    for (int j = 0; j < pool; j++) {
-      const int p = blk * pool + j;
-      const int page = block_table[(size_t)b * bt_width + p / page_size];
-      if (page < 0) continue;
-      const int in_page = p % page_size;
-      if (i < hd) s += to_f32(k_pool[(((size_t)page * nkv + kvh) * page_size + in_page) * hd + i]);
-      else s += to_f32(v_pool[(((size_t)page * nkv + kvh) * vd + (i - hd)) * page_size + in_page]);
+    for (int j0 = 0; j0 < pool; j0 += 8) {      // eight loads in flight, added in the order of the positions
+      float t[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int p = blk * pool + j0 + u;
+        const int page = j0 + u < pool ? block_table[(size_t)b * bt_width + p / page_size] : -1;
+        const int in_page = p % page_size;
+        t[u] = page < 0 ? 0.f
+               : i < hd ? to_f32(k_pool[(((size_t)page * nkv + kvh) * page_size + in_page) * hd + i])
+                        : to_f32(v_pool[(((size_t)page * nkv + kvh) * vd + (i - hd)) * page_size + in_page]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) s += t[u];
     }
     if (i < hd) pk_pool[(((size_t)ppage * nkv + kvh) * page_size + pin) * hd + i] = from_f32<T>(s * inv);
     else pv_pool[(((size_t)ppage * nkv + kvh) * vd + (i - hd)) * page_size + pin] = from_f32<T>(s * inv);
@@ -212,8 +222,8 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
 
   float* q_s = sm;                 // [R][hd]
   float* k_s = q_s + R * hd;       // [32][hd + 1]
-  float* v_s = k_s + 32 * KS;      // [32][vd]
-  float* p_s = v_s + 32 * vd;      // [PAT_WARPS][32]
+  float* v_s = k_s + 32 * KS;      // [vd][33]: a dimension's 32 positions of the tile
+  float* p_s = v_s + 33 * vd;      // [PAT_WARPS][32]
   float* o_s = p_s + PAT_WARPS * 32;   // [PAT_WARPS][vd]
 
   if (slot < 0) {  // padding sequence: defined output, no cache access
@@ -275,17 +285,53 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
     const size_t base = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * page_size + key0 % page_size) * hd;
     const size_t vbase = ((size_t)(page < 0 ? 0 : page) * nkv + kvh) * vd * page_size + key0 % page_size;
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 32 * hd; idx += blockDim.x) {
-      const int kk = idx / hd, d = idx - kk * hd;
-      float kv = 0.f;
-      if (page >= 0 && key0 + kk < limit) kv = to_f32(kp[base + idx]);
-      k_s[kk * KS + d] = kv;
-    }
-    for (int idx = threadIdx.x; idx < 32 * vd; idx += blockDim.x) {
-      const int d = idx / 32, kk = idx - d * 32;
-      float vv = 0.f;
-      if (page >= 0 && key0 + kk < limit) vv = to_f32(vp[vbase + (size_t)d * page_size + kk]);
-      v_s[kk * vd + d] = vv;
+    constexpr int EV = 16 / (int)sizeof(CT);      // cached numbers in a 16-byte load
+    if (hd % EV == 0) {
+      // the tile's keys are one contiguous run, a dimension's 32 values another: 16-byte loads, two of each
+      // kind in flight per thread before anything is stored
+      const int nvk = 32 * hd / EV, nvv = vd * (32 / EV);
+      for (int i0 = 0; i0 < max(nvk, nvv); i0 += 2 * blockDim.x) {
+        uint4 rk[2], rv[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int idx = i0 + u * blockDim.x + threadIdx.x;
+          rk[u] = make_uint4(0, 0, 0, 0);
+          rv[u] = make_uint4(0, 0, 0, 0);
+          if (page >= 0 && idx < nvk && key0 + idx * EV / hd < limit)
+            rk[u] = *reinterpret_cast<const uint4*>(kp + base + (size_t)idx * EV);
+          if (page >= 0 && idx < nvv)
+            rv[u] = *reinterpret_cast<const uint4*>(vp + vbase + (size_t)(idx / (32 / EV)) * page_size + (idx % (32 / EV)) * EV);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int idx = i0 + u * blockDim.x + threadIdx.x;
+          if (idx < nvk) {
+            const int kk = idx * EV / hd, d = idx * EV - kk * hd;
+            const CT* el = reinterpret_cast<const CT*>(&rk[u]);
+#pragma unroll
+            for (int j = 0; j < EV; j++) k_s[kk * KS + d + j] = to_f32(el[j]);
+          }
+          if (idx < nvv) {
+            const int d = idx / (32 / EV), k0 = (idx % (32 / EV)) * EV;
+            const CT* el = reinterpret_cast<const CT*>(&rv[u]);
+#pragma unroll
+            for (int j = 0; j < EV; j++) v_s[d * 33 + k0 + j] = (key0 + k0 + j < limit) ? to_f32(el[j]) : 0.f;
+          }
+        }
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < 32 * hd; idx += blockDim.x) {
+        const int kk = idx / hd, d = idx - kk * hd;
+        float kv = 0.f;
+        if (page >= 0 && key0 + kk < limit) kv = to_f32(kp[base + idx]);
+        k_s[kk * KS + d] = kv;
+      }
+      for (int idx = threadIdx.x; idx < 32 * vd; idx += blockDim.x) {
+        const int d = idx / 32, kk = idx - d * 32;
+        float vv = 0.f;
+        if (page >= 0 && key0 + kk < limit) vv = to_f32(vp[vbase + (size_t)d * page_size + kk]);
+        v_s[d * 33 + kk] = vv;
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -318,7 +364,7 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
         if (d < vd) {
           float a = 0.f;
 #pragma unroll 8
-          for (int kk = 0; kk < 32; kk++) a += p_s[warp * 32 + kk] * v_s[kk * vd + d];
+          for (int kk = 0; kk < 32; kk++) a += p_s[warp * 32 + kk] * v_s[d * 33 + kk];
           acc[ri][jj] = acc[ri][jj] * corr + a;
         }
       }
@@ -419,7 +465,7 @@ static int launch_attention_pooled(void* out, float* part, const void* q, const 
   if (QT > max_qlen) QT = max_qlen;
   const int R = QT * HC;
   const int n_hc = ceil_div(G, HC);
-  const size_t smem = ((size_t)R * hd + 32 * (hd + 1) + 32 * vd + PAT_WARPS * 32 + PAT_WARPS * vd) * sizeof(float);
+  const size_t smem = ((size_t)R * hd + 32 * (hd + 1) + 33 * vd + PAT_WARPS * 32 + PAT_WARPS * vd) * sizeof(float);
   auto kern = attention_pooled_kernel<T, CT, HDL>;
   static size_t smem_set = 0;
   if (smem > 48 * 1024 && smem > smem_set) {

@@ -14,8 +14,7 @@
 // (head h reads key head h / (H / Gk)).
 //
 // The columns of S never mix, so a warp owns one column (lane r holds rows r, r + 32, ...) and walks
-// the sequence's rows of the step in order; k, q, a, v and w of the next row are fetched while the
-// current one is computed.  The state is kept [slot][head][column][row] so that a warp's column is
+// the sequence's rows of the step in order; k, q, a, v and w of the rows come through shared memory.  The state is kept [slot][head][column][row] so that a warp's column is
 // one contiguous run.  The same kernel serves prompts, portions and decode steps: a row's result
 // depends only on the state before it and the rows of its own sequence.
 #include "common.cuh"
@@ -26,23 +25,40 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + lo
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
+constexpr int REC_ROWS = 8;       // rows of the step whose operands are staged at once
+
+__device__ __forceinline__ void rec_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rec_copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rec_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void rec_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A block is REC_WARPS columns of one head of one sequence.  Its warps read the same k, q and decay of a row,
+// so the rows' operands come in through shared memory, REC_ROWS rows at a time in two buffers: the copies of
+// the next rows are in flight while these are computed, and the walk over the rows never waits on global
+// memory (a walk that fetched one row ahead into registers was bound by that latency, row after row).
 template <int RL, bool DELTA, bool ROW_DECAY>
 __global__ void __launch_bounds__(32 * REC_WARPS)
 gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restrict__ k, const float* __restrict__ q, int ldk,
                         const float* __restrict__ v, int ldv, const float* __restrict__ wr, int ldw,
                         const float* __restrict__ decay, int ldd, const float* __restrict__ skip,
                         float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
-                        const int* __restrict__ seq_qlen, int H, int Gk, int d, int e) {
+                        const int* __restrict__ seq_qlen, int H, int Gk, int d, int e, int wide) {
+  extern __shared__ float rec_sm[];
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c = blockIdx.x * REC_WARPS + warp;
-  if (c >= e) return;
+  const int c0 = blockIdx.x * REC_WARPS, c = c0 + warp;
+  const bool active = c < e;
   const int h = blockIdx.y, b = blockIdx.z;
   const int slot = seq_slot[b];
   const int n = seq_qlen ? seq_qlen[b] : 1;
   const int m0 = seq_qstart[b];
   const int kh = h / (H / Gk);
-  float* sp = slot >= 0 ? state + (((size_t)slot * H + h) * e + c) * d : nullptr;
+  float* sp = (slot >= 0 && active) ? state + (((size_t)slot * H + h) * e + c) * d : nullptr;
   float s[RL];
 #pragma unroll
   for (int i = 0; i < RL; i++) {
@@ -50,57 +66,90 @@ gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restric
     s[i] = (sp && r < d) ? sp[r] : 0.f;
   }
   const float sk = skip ? skip[h] : 0.f;
-  // the first row's operands
-  float kc[RL], qc[RL], ac[RL], vc, wc;
-  {
-    const size_t m = m0;
-#pragma unroll
-    for (int i = 0; i < RL; i++) {
-      const int r = lane + 32 * i;
-      const bool in = r < d && n > 0;
-      kc[i] = in ? k[m * ldk + kh * d + r] : 0.f;
-      qc[i] = in ? q[m * ldk + kh * d + r] : 0.f;
-      ac[i] = in ? (ROW_DECAY ? decay[m * ldd + h * d + r] : decay[m * ldd + h]) : 0.f;
+  // one buffer: k [REC_ROWS][d] | q [REC_ROWS][d] | decay [REC_ROWS][d or 1] | v [REC_ROWS][REC_WARPS] | write [REC_ROWS]
+  const int da = ROW_DECAY ? d : 1;
+  const int stage = REC_ROWS * (2 * d + da + REC_WARPS + 1);
+  auto fetch = [&](int ch) {
+    float* ks = rec_sm + (ch & 1) * stage;
+    float* qs = ks + REC_ROWS * d;
+    float* as = qs + REC_ROWS * d;
+    float* vs = as + REC_ROWS * da;
+    float* ws = vs + REC_ROWS * REC_WARPS;
+    const int rows = min(REC_ROWS, n - ch * REC_ROWS);
+    const size_t m = (size_t)m0 + (size_t)ch * REC_ROWS;
+    if (wide) {      // every run starts on 16 bytes and d is a multiple of 4
+      const int per = d / 4;
+      for (int idx = threadIdx.x; idx < rows * per; idx += blockDim.x) {
+        const int t = idx / per, j = (idx - t * per) * 4;
+        rec_copy16(ks + t * d + j, k + (m + t) * ldk + kh * d + j);
+        rec_copy16(qs + t * d + j, q + (m + t) * ldk + kh * d + j);
+        if (ROW_DECAY) rec_copy16(as + t * d + j, decay + (m + t) * ldd + h * d + j);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < rows * d; idx += blockDim.x) {
+        const int t = idx / d, j = idx - t * d;
+        rec_copy4(ks + idx, k + (m + t) * ldk + kh * d + j);
+        rec_copy4(qs + idx, q + (m + t) * ldk + kh * d + j);
+        if (ROW_DECAY) rec_copy4(as + idx, decay + (m + t) * ldd + h * d + j);
+      }
     }
-    vc = n > 0 ? v[m * ldv + h * e + c] : 0.f;
-    wc = n > 0 ? wr[m * ldw + h] : 0.f;
-  }
-  for (int t = 0; t < n; t++) {
-    const size_t m = (size_t)m0 + t;
-    float kn[RL], qn[RL], an[RL], vn = 0.f, wn = 0.f;
-    const bool more = t + 1 < n;
-#pragma unroll
-    for (int i = 0; i < RL; i++) {
-      const int r = lane + 32 * i;
-      const bool in = more && r < d;
-      kn[i] = in ? k[(m + 1) * ldk + kh * d + r] : 0.f;
-      qn[i] = in ? q[(m + 1) * ldk + kh * d + r] : 0.f;
-      an[i] = in ? (ROW_DECAY ? decay[(m + 1) * ldd + h * d + r] : decay[(m + 1) * ldd + h]) : 0.f;
+    for (int idx = threadIdx.x; idx < rows * (REC_WARPS + 2); idx += blockDim.x) {
+      const int t = idx / (REC_WARPS + 2), j = idx - t * (REC_WARPS + 2);
+      if (j < REC_WARPS) {
+        if (c0 + j < e) rec_copy4(vs + t * REC_WARPS + j, v + (m + t) * ldv + h * e + c0 + j);
+      } else if (j == REC_WARPS) {
+        rec_copy4(ws + t, wr + (m + t) * ldw + h);
+      } else if (!ROW_DECAY) {
+        rec_copy4(as + t, decay + (m + t) * ldd + h);
+      }
     }
-    if (more) {
-      vn = v[(m + 1) * ldv + h * e + c];
-      wn = wr[(m + 1) * ldw + h];
+    rec_commit();
+  };
+  const int n_chunks = (n + REC_ROWS - 1) / REC_ROWS;
+  if (n_chunks > 0) fetch(0);
+  for (int ch = 0; ch < n_chunks; ch++) {
+    if (ch + 1 < n_chunks) {
+      fetch(ch + 1);
+      rec_wait<1>();
+    } else {
+      rec_wait<0>();
     }
-    float dot = 0.f;
+    __syncthreads();
+    const float* ks = rec_sm + (ch & 1) * stage;
+    const float* qs = ks + REC_ROWS * d;
+    const float* as = qs + REC_ROWS * d;
+    const float* vs = as + REC_ROWS * da;
+    const float* ws = vs + REC_ROWS * REC_WARPS;
+    const int rows = min(REC_ROWS, n - ch * REC_ROWS);
+    if (active) {
+      for (int t = 0; t < rows; t++) {
+        const size_t m = (size_t)m0 + (size_t)ch * REC_ROWS + t;
+        float kc[RL], qc[RL];
+        const float vc = vs[t * REC_WARPS + warp], wc = ws[t];
+        float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < RL; i++) {
-      s[i] *= ac[i];
-      if (DELTA) dot += s[i] * kc[i];
+        for (int i = 0; i < RL; i++) {
+          const int r = lane + 32 * i;
+          const bool in = r < d;
+          kc[i] = in ? ks[t * d + r] : 0.f;
+          qc[i] = in ? qs[t * d + r] : 0.f;
+          const float ac = ROW_DECAY ? (in ? as[t * d + r] : 0.f) : as[t];
+          s[i] *= ac;
+          if (DELTA) dot += s[i] * kc[i];
+        }
+        float u = wc * vc;
+        if (DELTA) u = wc * (vc - warp_sum(dot));
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < RL; i++) {
+          s[i] += kc[i] * u;
+          o += s[i] * qc[i];
+        }
+        o = warp_sum(o);
+        if (lane == 0) out[m * ldo + h * e + c] = o + sk * vc;
+      }
     }
-    float u = wc * vc;
-    if (DELTA) u = wc * (vc - warp_sum(dot));
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < RL; i++) {
-      s[i] += kc[i] * u;
-      o += s[i] * qc[i];
-    }
-    o = warp_sum(o);
-    if (lane == 0) out[m * ldo + h * e + c] = o + sk * vc;
-#pragma unroll
-    for (int i = 0; i < RL; i++) { kc[i] = kn[i]; qc[i] = qn[i]; ac[i] = an[i]; }
-    vc = vn;
-    wc = wn;
+    __syncthreads();      // the buffer is free for the rows after the next
   }
   if (sp) {
 #pragma unroll
@@ -122,15 +171,28 @@ LEB_API int leb_gated_recurrence(float* out, int ldo, const float* k, const floa
   LEB_REQUIRE(d >= 1 && d <= 256 && e >= 1, "leb_gated_recurrence: a state of %d x %d (rows 1..256)", d, e);
   LEB_REQUIRE(H <= 65535 && B <= 65535, "leb_gated_recurrence: step too large");
   const dim3 grid(ceil_div(e, REC_WARPS), H, B), block(32 * REC_WARPS);
+  const size_t smem = (size_t)2 * REC_ROWS * (2 * d + (row_decay ? d : 1) + REC_WARPS + 1) * sizeof(float);
+  // 16-byte copies when every run of k, q and the decay starts on 16 bytes
+  const int wide = d % 4 == 0 && ldk % 4 == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
+                   (!row_decay || (ldd % 4 == 0 && ((uintptr_t)decay & 15) == 0));
   LebPlainLaunches plain(true);
-#define LEB_REC3(RL_, D_, R_) leb_launch(gated_recurrence_kernel<RL_, D_, R_>, grid, block, 0, st, out, ldo, k, q, ldk, v, ldv, \
-                                         write, ldw, decay, ldd, skip, state, seq_slot, seq_qstart, seq_qlen, H, Gk, d, e)
+#define LEB_REC3(RL_, D_, R_)                                                                                            \
+  {                                                                                                                      \
+    static size_t set = 48 * 1024;                                                                                       \
+    if (smem > set) {                                                                                                    \
+      if (cudaFuncSetAttribute(gated_recurrence_kernel<RL_, D_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        return leb_fail("leb_gated_recurrence: %zu bytes of shared memory per block refused", smem);                    \
+      set = smem;                                                                                                        \
+    }                                                                                                                    \
+    leb_launch(gated_recurrence_kernel<RL_, D_, R_>, grid, block, smem, st, out, ldo, k, q, ldk, v, ldv, write, ldw, decay, \
+               ldd, skip, state, seq_slot, seq_qstart, seq_qlen, H, Gk, d, e, wide);                                     \
+  }
 #define LEB_REC2(RL_)                                     \
   {                                                       \
-    if (delta && row_decay) LEB_REC3(RL_, true, true);    \
-    else if (delta) LEB_REC3(RL_, true, false);           \
-    else if (row_decay) LEB_REC3(RL_, false, true);       \
-    else LEB_REC3(RL_, false, false);                     \
+    if (delta && row_decay) LEB_REC3(RL_, true, true)     \
+    else if (delta) LEB_REC3(RL_, true, false)            \
+    else if (row_decay) LEB_REC3(RL_, false, true)        \
+    else LEB_REC3(RL_, false, false)                      \
   }
   if (d <= 32) LEB_REC2(1)
   else if (d <= 64) LEB_REC2(2)
@@ -147,6 +209,9 @@ LEB_API int leb_gated_recurrence(float* out, int ldo, const float* k, const floa
 //   v: silu;  write = sigmoid(b);  decay = exp(-exp(A_log_h) softplus(a + dt_bias)) per head and key channel
 // qk [M, 2*Gk*d + H*e] is the convolution's output (q | k | v), `a` [M, H*d] the decay's pre-activation and
 // `b` [M, H] the write strength's (row strides lda, ldb).  Results: qn, kn [M, Gk*d], vs [M, H*e], g [M, H*d], wr [M, H].
+// A row's work is spread over blockIdx.y: first blocks of four heads of q | k (a warp a head), then blocks of
+// DPREP_CHUNK numbers of v | decay | write, so that a decode step of a few rows still fills the machine.
+constexpr int DPREP_CHUNK = 512;
 __global__ void __launch_bounds__(128)
 delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vs, float* __restrict__ g,
                   float* __restrict__ wr, const float* __restrict__ qkv, int ldq, const float* __restrict__ a, int lda,
@@ -156,7 +221,10 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
   const size_t m = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float* row = qkv + m * ldq;
-  for (int hh = warp; hh < 2 * Gk; hh += nw) {      // heads of q, then heads of k
+  const int head_blocks = (2 * Gk + nw - 1) / nw;
+  if ((int)blockIdx.y < head_blocks) {      // heads of q, then heads of k
+    const int hh = blockIdx.y * nw + warp;
+    if (hh >= 2 * Gk) return;
     const float* src = row + (size_t)hh * d;
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) {
@@ -167,14 +235,23 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
     const float r = 1.0f / sqrtf(ss + unit_eps) * (hh < Gk ? q_scale : 1.0f);
     float* dst = hh < Gk ? qn + m * (size_t)(Gk * d) + (size_t)hh * d : kn + m * (size_t)(Gk * d) + (size_t)(hh - Gk) * d;
     for (int i = lane; i < d; i += 32) dst[i] = silu_f(src[i]) * r;
+    return;
   }
   const float* vrow = row + (size_t)2 * Gk * d;
-  for (int i = threadIdx.x; i < H * e; i += blockDim.x) vs[m * (size_t)(H * e) + i] = silu_f(vrow[i]);
-  for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
-    const float rate = expf(A_log[i / d]);
-    g[m * (size_t)(H * d) + i] = expf(-rate * softplus_f(a[m * lda + i] + dt_bias[i]));
+  const int nv = H * e, ng = H * d;
+  const int lo = ((int)blockIdx.y - head_blocks) * DPREP_CHUNK, hi = min(lo + DPREP_CHUNK, nv + ng + H);
+  for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+    if (j < nv) {
+      vs[m * (size_t)nv + j] = silu_f(vrow[j]);
+    } else if (j < nv + ng) {
+      const int i = j - nv;
+      const float rate = expf(A_log[i / d]);
+      g[m * (size_t)ng + i] = expf(-rate * softplus_f(a[m * lda + i] + dt_bias[i]));
+    } else {
+      const int i = j - nv - ng;
+      wr[m * H + i] = sigmoid_f(bw[m * ldb + i]);
+    }
   }
-  for (int i = threadIdx.x; i < H; i += blockDim.x) wr[m * H + i] = sigmoid_f(bw[m * ldb + i]);
 }
 
 LEB_API int leb_delta_prep(float* qn, float* kn, float* vs, float* g, float* wr, const float* qkv, int ldq, const float* a,
@@ -182,8 +259,10 @@ LEB_API int leb_delta_prep(float* qn, float* kn, float* vs, float* g, float* wr,
                            int d, int e, float unit_eps, float q_scale, cudaStream_t st) {
   if (M <= 0) return 0;
   LebPlainLaunches plain(true);
-  leb_launch(delta_prep_kernel, dim3(M), dim3(128), 0, st, qn, kn, vs, g, wr, qkv, ldq, a, lda, bw, ldb, dt_bias, A_log,
-             H, Gk, d, e, unit_eps, q_scale);
+  const int blocks_y = ceil_div(2 * Gk, 4) + ceil_div(H * e + H * d + H, DPREP_CHUNK);
+  LEB_REQUIRE(blocks_y <= 65535, "leb_delta_prep: a row of %d blocks", blocks_y);
+  leb_launch(delta_prep_kernel, dim3(M, blocks_y), dim3(128), 0, st, qn, kn, vs, g, wr, qkv, ldq, a, lda, bw, ldb, dt_bias,
+             A_log, H, Gk, d, e, unit_eps, q_scale);
   LEB_CHECK_LAUNCH("leb_delta_prep");
   return 0;
 }
@@ -197,10 +276,11 @@ ssm_prep_kernel(float* __restrict__ xbc, int ldx, int C, const float* __restrict
                 const float* __restrict__ A_log, int H) {
   pdl_wait();
   const size_t m = blockIdx.x;
-  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < C; i += gridDim.y * blockDim.x) {
     const float x = xbc[m * ldx + i] + (conv_bias ? conv_bias[i] : 0.f);
     xbc[m * ldx + i] = silu_f(x);
   }
+  if (blockIdx.y != 0) return;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     const float t = softplus_f(dt_raw[m * ldt + i] + dt_bias[i]);
     dt[m * H + i] = t;
@@ -212,7 +292,9 @@ LEB_API int leb_ssm_prep(float* xbc, int ldx, int C, const float* conv_bias, flo
                          int ldt, const float* dt_bias, const float* A_log, int M, int H, cudaStream_t st) {
   if (M <= 0) return 0;
   LebPlainLaunches plain(true);
-  leb_launch(ssm_prep_kernel, dim3(M), dim3(128), 0, st, xbc, ldx, C, conv_bias, dt, decay, dt_raw, ldt, dt_bias, A_log, H);
+  const int blocks_y = min(ceil_div(C, 4 * 128), 64);      // a thread takes about four channels
+  leb_launch(ssm_prep_kernel, dim3(M, blocks_y), dim3(128), 0, st, xbc, ldx, C, conv_bias, dt, decay, dt_raw, ldt, dt_bias,
+             A_log, H);
   LEB_CHECK_LAUNCH("leb_ssm_prep");
   return 0;
 }
@@ -221,31 +303,44 @@ LEB_API int leb_ssm_prep(float* xbc, int ldx, int C, const float* conv_bias, flo
 // row are divided by their root mean square (eps inside the root) and multiplied by a weight
 // (w[j % wlen]: one weight for every group, or one per column), and the row is gated by a second
 // row z: sigmoid(z) after the norm (gate_first = 0), or silu(z) before it (gate_first = 1).
-// y, z float; out in the activation type.  A warp takes a group.
+// y, z float; out in the activation type.  A team takes a group: a warp (four groups a block, blockIdx.y counts
+// blocks of groups), or for groups wider than GNG_WARP_MAX the whole block (blockIdx.y is the group).
+constexpr int GNG_WARP_MAX = 256;
 template <typename T>
 __global__ void __launch_bounds__(128)
 group_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ y, const float* __restrict__ z, int ldz,
                        const float* __restrict__ w, int C, int gs, int wlen, float eps, int gate_first) {
+  __shared__ float red[4];
   pdl_wait();
   const size_t m = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int gidx = warp; gidx < C / gs; gidx += nw) {
-    const float* yr = y + m * C + (size_t)gidx * gs;
-    const float* zr = z + m * ldz + (size_t)gidx * gs;
-    float ss = 0.f;
-    for (int i = lane; i < gs; i += 32) {
+  const bool wide = gs > GNG_WARP_MAX;
+  const int gidx = wide ? blockIdx.y : blockIdx.y * nw + warp;
+  const int t0 = wide ? threadIdx.x : lane, nt = wide ? blockDim.x : 32;
+  const bool live = gidx < C / gs;     // only a warp-sized team can be idle: no block-wide wait follows for it
+  const float* yr = y + m * C + (size_t)gidx * gs;
+  const float* zr = z + m * ldz + (size_t)gidx * gs;
+  float ss = 0.f;
+  if (live)
+    for (int i = t0; i < gs; i += nt) {
       const float x = gate_first ? yr[i] * silu_f(zr[i]) : yr[i];
       ss += x * x;
     }
-    ss = warp_sum(ss);
-    const float r = 1.0f / sqrtf(ss / (float)gs + eps);
-    for (int i = lane; i < gs; i += 32) {
-      const int j = gidx * gs + i;
-      const float x = gate_first ? yr[i] * silu_f(zr[i]) : yr[i];
-      float val = x * r * w[j % wlen];
-      if (!gate_first) val *= sigmoid_f(zr[i]);
-      out[m * C + j] = from_f32<T>(val);
-    }
+  ss = warp_sum(ss);
+  if (wide) {
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int i = 0; i < nw; i++) ss += red[i];     // the same order in every thread
+  }
+  if (!live) return;
+  const float r = 1.0f / sqrtf(ss / (float)gs + eps);
+  for (int i = t0; i < gs; i += nt) {
+    const int j = gidx * gs + i;
+    const float x = gate_first ? yr[i] * silu_f(zr[i]) : yr[i];
+    float val = x * r * w[j % wlen];
+    if (!gate_first) val *= sigmoid_f(zr[i]);
+    out[m * C + j] = from_f32<T>(val);
   }
 }
 
@@ -254,10 +349,13 @@ LEB_API int leb_group_norm_gate(void* out, int dtype, const float* y, const floa
   if (M <= 0) return 0;
   LEB_REQUIRE(gs >= 1 && C % gs == 0 && wlen >= 1, "leb_group_norm_gate: %d columns in groups of %d", C, gs);
   LebPlainLaunches plain(true);
+  const int groups = C / gs;
+  const dim3 grid(M, gs > GNG_WARP_MAX ? groups : ceil_div(groups, 4));
+  LEB_REQUIRE(grid.y <= 65535, "leb_group_norm_gate: %d groups in a row", groups);
   if (dtype == LEB_F32)
-    leb_launch(group_norm_gate_kernel<float>, dim3(M), dim3(128), 0, st, (float*)out, y, z, ldz, w, C, gs, wlen, eps, gate_first);
+    leb_launch(group_norm_gate_kernel<float>, grid, dim3(128), 0, st, (float*)out, y, z, ldz, w, C, gs, wlen, eps, gate_first);
   else if (dtype == LEB_BF16)
-    leb_launch(group_norm_gate_kernel<bf16>, dim3(M), dim3(128), 0, st, (bf16*)out, y, z, ldz, w, C, gs, wlen, eps, gate_first);
+    leb_launch(group_norm_gate_kernel<bf16>, grid, dim3(128), 0, st, (bf16*)out, y, z, ldz, w, C, gs, wlen, eps, gate_first);
   else
     return leb_fail("leb_group_norm_gate: unknown dtype %d", dtype);
   LEB_CHECK_LAUNCH("leb_group_norm_gate");
