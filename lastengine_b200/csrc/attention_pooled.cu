@@ -73,22 +73,24 @@ pooled_prep_kernel(T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict_
       nrot = vd;
       freq = freq_v;
     }
+    if (!freq) nrot = 0;
     const int half = nrot / 2;
-    for (int i = lane; i < width; i += 32) {
-      float val = buf[i];
-      if (i < nrot && freq) {
-        const int pr = i < half ? i : i - half;
-        float sn, cs;
-        sincosf(fpos * freq[pr], &sn, &cs);
-        val = i < half ? buf[i] * cs - buf[i + half] * sn : buf[i] * cs + buf[i - half] * sn;
-      }
+    auto put = [&](int i, float val) {
       if (is_q) {
         q_out[(m * nh + hh) * hd + i] = from_f32<T>(val);
       } else if (page >= 0) {
         if (is_k) k_pool[(((size_t)page * nkv + (hh - nh)) * page_size + in_page) * hd + i] = from_f32<T>(val);
         else v_pool[(((size_t)page * nkv + (hh - nh - nkv)) * vd + i) * page_size + in_page] = from_f32<T>(val);
       }
+    };
+    for (int i = lane; i < half; i += 32) {      // a pair (i, i + half) shares its angle
+      float sn, cs;
+      sincosf(fpos * freq[i], &sn, &cs);
+      const float lo = buf[i], hi = buf[i + half];
+      put(i, lo * cs - hi * sn);
+      put(i + half, hi * cs + lo * sn);
     }
+    for (int i = nrot + lane; i < width; i += 32) put(i, buf[i]);
     __syncwarp();
   }
 }

@@ -13,19 +13,20 @@
 // in this order: the read-out sees the row's own write.  Several heads may share one key/query head
 // (head h reads key head h / (H / Gk)).
 //
-// The columns of S never mix, so a warp owns one column (lane r holds rows r, r + 32, ...) and walks
-// the sequence's rows of the step in order; k, q, a, v and w of the rows come through shared memory.  The state is kept [slot][head][column][row] so that a warp's column is
+// The columns of S never mix, so eight lanes own one column and walk the sequence's rows of the step in
+// order; k, q, a, v and w of the rows come through shared memory.  The state is kept [slot][head][column][row] so that a warp's column is
 // one contiguous run.  The same kernel serves prompts, portions and decode steps: a row's result
 // depends only on the state before it and the rows of its own sequence.
 #include "common.cuh"
 
-constexpr int REC_WARPS = 8;      // columns per block
+constexpr int REC_WARPS = 4;      // warps of a block
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
 constexpr int REC_ROWS = 8;       // rows of the step whose operands are staged at once
+constexpr int REC_COLS = 4 * REC_WARPS;   // columns of a block: a warp walks four, eight lanes each
 
 __device__ __forceinline__ void rec_copy4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -36,22 +37,34 @@ __device__ __forceinline__ void rec_copy16(float* dst, const float* src) {
 __device__ __forceinline__ void rec_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void rec_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ float sum8(float x) {      // over the eight lanes of a column
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  return x;
+}
 
-// A block is REC_WARPS columns of one head of one sequence.  Its warps read the same k, q and decay of a row,
-// so the rows' operands come in through shared memory, REC_ROWS rows at a time in two buffers: the copies of
-// the next rows are in flight while these are computed, and the walk over the rows never waits on global
-// memory (a walk that fetched one row ahead into registers was bound by that latency, row after row).
-template <int RL, bool DELTA, bool ROW_DECAY>
+// A block is REC_COLS columns of one head of one sequence.  Eight lanes hold a column: lane j the rows
+// 4 (j + 8 i) .. + 3 for i < NV, so a warp walks four columns, reads k, q and the decay of a row as 16-byte
+// pieces that its four column groups share, and sums over a column in three exchanges.  The rows' operands
+// come in through shared memory, REC_ROWS rows at a time in two buffers: the copies of the next rows are in
+// flight while these are computed, and the walk over the rows never waits on global memory.  A staged row is
+// padded with zeros to 32 NV numbers, so the walk has no bounds to test.
+template <int NV, bool DELTA, bool ROW_DECAY>
 __global__ void __launch_bounds__(32 * REC_WARPS)
 gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restrict__ k, const float* __restrict__ q, int ldk,
                         const float* __restrict__ v, int ldv, const float* __restrict__ wr, int ldw,
                         const float* __restrict__ decay, int ldd, const float* __restrict__ skip,
                         float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                         const int* __restrict__ seq_qlen, int H, int Gk, int d, int e, int wide) {
-  extern __shared__ float rec_sm[];
+  extern __shared__ __align__(16) float rec_sm[];
+  constexpr int DP = 32 * NV;                   // a staged row of k, q or the decay
+  constexpr int DA = ROW_DECAY ? DP : 1;
+  constexpr int STAGE = REC_ROWS * (2 * DP + REC_COLS) + ((REC_ROWS * (DA + 1) + 3) & ~3);
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = blockIdx.x * REC_WARPS, c = c0 + warp;
+  const int j8 = lane & 7, cb = warp * 4 + (lane >> 3);     // place in the column, column in the block
+  const int c0 = blockIdx.x * REC_COLS, c = c0 + cb;
   const bool active = c < e;
   const int h = blockIdx.y, b = blockIdx.z;
   const int slot = seq_slot[b];
@@ -59,45 +72,53 @@ gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restric
   const int m0 = seq_qstart[b];
   const int kh = h / (H / Gk);
   float* sp = (slot >= 0 && active) ? state + (((size_t)slot * H + h) * e + c) * d : nullptr;
-  float s[RL];
+  float s[4 * NV];
 #pragma unroll
-  for (int i = 0; i < RL; i++) {
-    const int r = lane + 32 * i;
-    s[i] = (sp && r < d) ? sp[r] : 0.f;
-  }
+  for (int i = 0; i < NV; i++)
+#pragma unroll
+    for (int x = 0; x < 4; x++) {
+      const int r = 4 * (j8 + 8 * i) + x;
+      s[4 * i + x] = (sp && r < d) ? sp[r] : 0.f;
+    }
   const float sk = skip ? skip[h] : 0.f;
-  // one buffer: k [REC_ROWS][d] | q [REC_ROWS][d] | decay [REC_ROWS][d or 1] | v [REC_ROWS][REC_WARPS] | write [REC_ROWS]
-  const int da = ROW_DECAY ? d : 1;
-  const int stage = REC_ROWS * (2 * d + da + REC_WARPS + 1);
+  // one buffer: k [REC_ROWS][DP] | q [REC_ROWS][DP] | v [REC_ROWS][REC_COLS] | decay [REC_ROWS][DA] | write [REC_ROWS]
+  for (int idx = threadIdx.x; idx < 2 * REC_ROWS * (DP - d); idx += blockDim.x) {      // the padding, once
+    const int st = idx / (REC_ROWS * (DP - d)), rest = idx - st * (REC_ROWS * (DP - d));
+    const int t = rest / (DP - d), jj = d + rest - t * (DP - d);
+    float* base = rec_sm + st * STAGE;
+    base[t * DP + jj] = 0.f;
+    base[REC_ROWS * DP + t * DP + jj] = 0.f;
+    if (ROW_DECAY) base[REC_ROWS * (2 * DP + REC_COLS) + t * DP + jj] = 0.f;
+  }
   auto fetch = [&](int ch) {
-    float* ks = rec_sm + (ch & 1) * stage;
-    float* qs = ks + REC_ROWS * d;
-    float* as = qs + REC_ROWS * d;
-    float* vs = as + REC_ROWS * da;
-    float* ws = vs + REC_ROWS * REC_WARPS;
+    float* ks = rec_sm + (ch & 1) * STAGE;
+    float* qs = ks + REC_ROWS * DP;
+    float* vs = qs + REC_ROWS * DP;
+    float* as = vs + REC_ROWS * REC_COLS;
+    float* ws = as + REC_ROWS * DA;
     const int rows = min(REC_ROWS, n - ch * REC_ROWS);
     const size_t m = (size_t)m0 + (size_t)ch * REC_ROWS;
     if (wide) {      // every run starts on 16 bytes and d is a multiple of 4
       const int per = d / 4;
       for (int idx = threadIdx.x; idx < rows * per; idx += blockDim.x) {
-        const int t = idx / per, j = (idx - t * per) * 4;
-        rec_copy16(ks + t * d + j, k + (m + t) * ldk + kh * d + j);
-        rec_copy16(qs + t * d + j, q + (m + t) * ldk + kh * d + j);
-        if (ROW_DECAY) rec_copy16(as + t * d + j, decay + (m + t) * ldd + h * d + j);
+        const int t = idx / per, jj = (idx - t * per) * 4;
+        rec_copy16(ks + t * DP + jj, k + (m + t) * ldk + kh * d + jj);
+        rec_copy16(qs + t * DP + jj, q + (m + t) * ldk + kh * d + jj);
+        if (ROW_DECAY) rec_copy16(as + t * DP + jj, decay + (m + t) * ldd + h * d + jj);
       }
     } else {
       for (int idx = threadIdx.x; idx < rows * d; idx += blockDim.x) {
-        const int t = idx / d, j = idx - t * d;
-        rec_copy4(ks + idx, k + (m + t) * ldk + kh * d + j);
-        rec_copy4(qs + idx, q + (m + t) * ldk + kh * d + j);
-        if (ROW_DECAY) rec_copy4(as + idx, decay + (m + t) * ldd + h * d + j);
+        const int t = idx / d, jj = idx - t * d;
+        rec_copy4(ks + t * DP + jj, k + (m + t) * ldk + kh * d + jj);
+        rec_copy4(qs + t * DP + jj, q + (m + t) * ldk + kh * d + jj);
+        if (ROW_DECAY) rec_copy4(as + t * DP + jj, decay + (m + t) * ldd + h * d + jj);
       }
     }
-    for (int idx = threadIdx.x; idx < rows * (REC_WARPS + 2); idx += blockDim.x) {
-      const int t = idx / (REC_WARPS + 2), j = idx - t * (REC_WARPS + 2);
-      if (j < REC_WARPS) {
-        if (c0 + j < e) rec_copy4(vs + t * REC_WARPS + j, v + (m + t) * ldv + h * e + c0 + j);
-      } else if (j == REC_WARPS) {
+    for (int idx = threadIdx.x; idx < rows * (REC_COLS + 2); idx += blockDim.x) {
+      const int t = idx / (REC_COLS + 2), jj = idx - t * (REC_COLS + 2);
+      if (jj < REC_COLS) {
+        if (c0 + jj < e) rec_copy4(vs + t * REC_COLS + jj, v + (m + t) * ldv + h * e + c0 + jj);
+      } else if (jj == REC_COLS) {
         rec_copy4(ws + t, wr + (m + t) * ldw + h);
       } else if (!ROW_DECAY) {
         rec_copy4(as + t, decay + (m + t) * ldd + h);
@@ -115,48 +136,79 @@ gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restric
       rec_wait<0>();
     }
     __syncthreads();
-    const float* ks = rec_sm + (ch & 1) * stage;
-    const float* qs = ks + REC_ROWS * d;
-    const float* as = qs + REC_ROWS * d;
-    const float* vs = as + REC_ROWS * da;
-    const float* ws = vs + REC_ROWS * REC_WARPS;
+    const float* ks = rec_sm + (ch & 1) * STAGE;
+    const float* qs = ks + REC_ROWS * DP;
+    const float* vs = qs + REC_ROWS * DP;
+    const float* as = vs + REC_ROWS * REC_COLS;
+    const float* ws = as + REC_ROWS * DA;
     const int rows = min(REC_ROWS, n - ch * REC_ROWS);
-    if (active) {
-      for (int t = 0; t < rows; t++) {
-        const size_t m = (size_t)m0 + (size_t)ch * REC_ROWS + t;
-        float kc[RL], qc[RL];
-        const float vc = vs[t * REC_WARPS + warp], wc = ws[t];
-        float dot = 0.f;
+    {
+      // Every lane walks (a column group beyond e computes on whatever its place of the buffer holds and stores
+      // nothing): the exchanges below name the whole warp.  The read-outs' sums over the lanes wait until the
+      // buffer's rows are done and then run side by side.
+      float o_part[REC_ROWS];
 #pragma unroll
-        for (int i = 0; i < RL; i++) {
-          const int r = lane + 32 * i;
-          const bool in = r < d;
-          kc[i] = in ? ks[t * d + r] : 0.f;
-          qc[i] = in ? qs[t * d + r] : 0.f;
-          const float ac = ROW_DECAY ? (in ? as[t * d + r] : 0.f) : as[t];
-          s[i] *= ac;
-          if (DELTA) dot += s[i] * kc[i];
+      for (int t = 0; t < REC_ROWS; t++) {
+        o_part[t] = 0.f;
+        if (t >= rows) continue;
+        const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP);
+        const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP);
+        const float4* a4 = reinterpret_cast<const float4*>(as + t * DP);
+        const float vc = vs[t * REC_COLS + cb], wc = ws[t];
+        const float a1 = ROW_DECAY ? 0.f : as[t];
+        float4 kv[NV], qv[NV];
+        float dp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+          kv[i] = k4[j8 + 8 * i];
+          qv[i] = q4[j8 + 8 * i];
+          float4 av = make_float4(a1, a1, a1, a1);
+          if (ROW_DECAY) av = a4[j8 + 8 * i];
+          s[4 * i + 0] *= av.x;
+          s[4 * i + 1] *= av.y;
+          s[4 * i + 2] *= av.z;
+          s[4 * i + 3] *= av.w;
+          if (DELTA) {
+            dp[0] = fmaf(s[4 * i + 0], kv[i].x, dp[0]);
+            dp[1] = fmaf(s[4 * i + 1], kv[i].y, dp[1]);
+            dp[2] = fmaf(s[4 * i + 2], kv[i].z, dp[2]);
+            dp[3] = fmaf(s[4 * i + 3], kv[i].w, dp[3]);
+          }
         }
         float u = wc * vc;
-        if (DELTA) u = wc * (vc - warp_sum(dot));
-        float o = 0.f;
+        if (DELTA) u = wc * (vc - sum8((dp[0] + dp[1]) + (dp[2] + dp[3])));
+        float op[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < RL; i++) {
-          s[i] += kc[i] * u;
-          o += s[i] * qc[i];
+        for (int i = 0; i < NV; i++) {
+          s[4 * i + 0] = fmaf(kv[i].x, u, s[4 * i + 0]);
+          s[4 * i + 1] = fmaf(kv[i].y, u, s[4 * i + 1]);
+          s[4 * i + 2] = fmaf(kv[i].z, u, s[4 * i + 2]);
+          s[4 * i + 3] = fmaf(kv[i].w, u, s[4 * i + 3]);
+          op[0] = fmaf(s[4 * i + 0], qv[i].x, op[0]);
+          op[1] = fmaf(s[4 * i + 1], qv[i].y, op[1]);
+          op[2] = fmaf(s[4 * i + 2], qv[i].z, op[2]);
+          op[3] = fmaf(s[4 * i + 3], qv[i].w, op[3]);
         }
-        o = warp_sum(o);
-        if (lane == 0) out[m * ldo + h * e + c] = o + sk * vc;
+        o_part[t] = (op[0] + op[1]) + (op[2] + op[3]);
+      }
+#pragma unroll
+      for (int t = 0; t < REC_ROWS; t++) o_part[t] = sum8(o_part[t]);
+#pragma unroll
+      for (int t = 0; t < REC_ROWS; t++) {
+        const size_t m = (size_t)m0 + (size_t)ch * REC_ROWS + t;
+        if (t < rows && j8 == 0 && active) out[m * ldo + h * e + c] = o_part[t] + sk * vs[t * REC_COLS + cb];
       }
     }
     __syncthreads();      // the buffer is free for the rows after the next
   }
   if (sp) {
 #pragma unroll
-    for (int i = 0; i < RL; i++) {
-      const int r = lane + 32 * i;
-      if (r < d) sp[r] = s[i];
-    }
+    for (int i = 0; i < NV; i++)
+#pragma unroll
+      for (int x = 0; x < 4; x++) {
+        const int r = 4 * (j8 + 8 * i) + x;
+        if (r < d) sp[r] = s[4 * i + x];
+      }
   }
 }
 
@@ -170,33 +222,34 @@ LEB_API int leb_gated_recurrence(float* out, int ldo, const float* k, const floa
   LEB_REQUIRE(H >= 1 && Gk >= 1 && H % Gk == 0, "leb_gated_recurrence: %d heads do not divide into %d key heads", H, Gk);
   LEB_REQUIRE(d >= 1 && d <= 256 && e >= 1, "leb_gated_recurrence: a state of %d x %d (rows 1..256)", d, e);
   LEB_REQUIRE(H <= 65535 && B <= 65535, "leb_gated_recurrence: step too large");
-  const dim3 grid(ceil_div(e, REC_WARPS), H, B), block(32 * REC_WARPS);
-  const size_t smem = (size_t)2 * REC_ROWS * (2 * d + (row_decay ? d : 1) + REC_WARPS + 1) * sizeof(float);
+  const dim3 grid(ceil_div(e, REC_COLS), H, B), block(32 * REC_WARPS);
+  const int nv = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8, dp = 32 * nv;
+  const size_t smem = (size_t)2 * (REC_ROWS * (2 * dp + REC_COLS) + ((REC_ROWS * ((row_decay ? dp : 1) + 1) + 3) & ~3)) * sizeof(float);
   // 16-byte copies when every run of k, q and the decay starts on 16 bytes
   const int wide = d % 4 == 0 && ldk % 4 == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
                    (!row_decay || (ldd % 4 == 0 && ((uintptr_t)decay & 15) == 0));
   LebPlainLaunches plain(true);
-#define LEB_REC3(RL_, D_, R_)                                                                                            \
+#define LEB_REC3(NV_, D_, R_)                                                                                            \
   {                                                                                                                      \
     static size_t set = 48 * 1024;                                                                                       \
     if (smem > set) {                                                                                                    \
-      if (cudaFuncSetAttribute(gated_recurrence_kernel<RL_, D_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      if (cudaFuncSetAttribute(gated_recurrence_kernel<NV_, D_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return leb_fail("leb_gated_recurrence: %zu bytes of shared memory per block refused", smem);                    \
       set = smem;                                                                                                        \
     }                                                                                                                    \
-    leb_launch(gated_recurrence_kernel<RL_, D_, R_>, grid, block, smem, st, out, ldo, k, q, ldk, v, ldv, write, ldw, decay, \
+    leb_launch(gated_recurrence_kernel<NV_, D_, R_>, grid, block, smem, st, out, ldo, k, q, ldk, v, ldv, write, ldw, decay, \
                ldd, skip, state, seq_slot, seq_qstart, seq_qlen, H, Gk, d, e, wide);                                     \
   }
-#define LEB_REC2(RL_)                                     \
+#define LEB_REC2(NV_)                                     \
   {                                                       \
-    if (delta && row_decay) LEB_REC3(RL_, true, true)     \
-    else if (delta) LEB_REC3(RL_, true, false)            \
-    else if (row_decay) LEB_REC3(RL_, false, true)        \
-    else LEB_REC3(RL_, false, false)                      \
+    if (delta && row_decay) LEB_REC3(NV_, true, true)     \
+    else if (delta) LEB_REC3(NV_, true, false)            \
+    else if (row_decay) LEB_REC3(NV_, false, true)        \
+    else LEB_REC3(NV_, false, false)                      \
   }
-  if (d <= 32) LEB_REC2(1)
-  else if (d <= 64) LEB_REC2(2)
-  else if (d <= 128) LEB_REC2(4)
+  if (nv == 1) LEB_REC2(1)
+  else if (nv == 2) LEB_REC2(2)
+  else if (nv == 4) LEB_REC2(4)
   else LEB_REC2(8)
 #undef LEB_REC2
 #undef LEB_REC3
