@@ -439,7 +439,7 @@ def _kisilix_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict
     W = cfg["width"]
     by = {"leb_postnorm_residual": 0, "leb_gated_act": 0, "leb_causal_conv": 0, "leb_delta_prep": 0, "leb_ssm_prep": 0,
           "leb_gated_recurrence": 0, "leb_group_norm_gate": 0, "leb_pooled_attn_prep": 0, "leb_attention_pooled": 0}
-    fl = {"leb_gated_recurrence": 0, "leb_attention_pooled": 0}
+    fl = {"leb_gated_recurrence": 0, "leb_attention_pooled": 0, "leb_attention_pooled_tc": 0}
     per_seq = rows // batch
     for l in cfg["layers"]:
         m = l["mixer"]
@@ -454,6 +454,7 @@ def _kisilix_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict
             seen = sum(_seen_keys(i, win, pool) for i in range(context - per_seq, context))
             fl["leb_attention_pooled"] += 2 * nh * (hd + vd) * seen * batch
             by["leb_attention_pooled"] += batch * _seen_keys(context - 1, win, pool) * nkv * (hd + vd) * 2 + rows * nh * (hd + vd) * 2
+            fl["leb_attention_pooled_tc"] = fl["leb_attention_pooled"]      # prompts at the tensor-core kernel's sizes
         else:
             delta = l["type"] == "channel_delta"
             H, e = m["heads"], m["vdim"]

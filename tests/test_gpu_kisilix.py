@@ -133,6 +133,7 @@ DELTA_CASES = [  # heads, kv heads, dim, vdim, taps
     (2, 2, 128, 64, 5),
     (1, 1, 40, 8, 3),
     (2, 1, 256, 16, 2),
+    (2, 1, 18, 10, 3),           # rows of a head that are no multiple of four numbers: the narrow copies
 ]
 
 
@@ -196,6 +197,8 @@ SSM_CASES = [  # heads, vdim, state, groups, norm parts, taps
     (2, 48, 16, 1, 4, 4),
     (4, 32, 256, 2, 1, 4),
     (6, 24, 128, 3, 6, 1),
+    (3, 6, 10, 1, 1, 2),         # B and C start off a 16-byte boundary in the convolved row
+    (6, 64, 32, 2, 1, 4),        # one norm group of 384 numbers: a whole block takes it
 ]
 
 
