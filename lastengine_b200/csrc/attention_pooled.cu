@@ -142,20 +142,26 @@ pool_blocks_kernel(T* __restrict__ pk_pool, T* __restrict__ pv_pool, const T* __
   const int pin = blk % page_size;
   const float inv = 1.0f / (float)pool;
   for (int i = threadIdx.x; i < hd + vd; i += blockDim.x) {
+    // one address form for a key's number and a value's, so that the loads carry no branch and eight are in flight
+    const bool is_k = i < hd;
+    const T* src = is_k ? k_pool + i : v_pool + (size_t)(i - hd) * page_size;
+    const size_t page_step = (size_t)nkv * page_size * (is_k ? hd : vd);
+    const size_t head_at = (size_t)kvh * page_size * (is_k ? hd : vd);
+    const int pos_step = is_k ? hd : 1;
     float s = 0.f;
-    for (int j0 = 0; j0 < pool; j0 += 8) {      // eight loads in flight, added in the order of the positions
+    for (int j0 = 0; j0 < pool; j0 += 8) {      // added in the order of the positions
+      int page[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++)
+        page[u] = j0 + u < pool ? block_table[(size_t)b * bt_width + (blk * pool + j0 + u) / page_size] : -1;
       float t[8];
 #pragma unroll
       for (int u = 0; u < 8; u++) {
-        const int p = blk * pool + j0 + u;
-        const int page = j0 + u < pool ? block_table[(size_t)b * bt_width + p / page_size] : -1;
-        const int in_page = p % page_size;
-        t[u] = page < 0 ? 0.f
-               : i < hd ? to_f32(k_pool[(((size_t)page * nkv + kvh) * page_size + in_page) * hd + i])
-                        : to_f32(v_pool[(((size_t)page * nkv + kvh) * vd + (i - hd)) * page_size + in_page]);
+        const int in_page = (blk * pool + j0 + u) % page_size;
+        t[u] = to_f32(src[(size_t)max(page[u], 0) * page_step + head_at + (size_t)in_page * pos_step]);
       }
 #pragma unroll
-      for (int u = 0; u < 8; u++) s += t[u];
+      for (int u = 0; u < 8; u++) s += page[u] >= 0 ? t[u] : 0.f;
     }
     if (i < hd) pk_pool[(((size_t)ppage * nkv + kvh) * page_size + pin) * hd + i] = from_f32<T>(s * inv);
     else pv_pool[(((size_t)ppage * nkv + kvh) * vd + (i - hd)) * page_size + pin] = from_f32<T>(s * inv);

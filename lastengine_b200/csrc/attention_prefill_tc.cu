@@ -79,7 +79,8 @@ __device__ __forceinline__ int atc_blocks_seen(int qpos, int window, int pool) {
   return (window > 0 && pool > 0 && past > 0) ? past / pool : 0;
 }
 
-template <int GS, bool POOLED>   // GS query heads per kv head (1, 2, 4, 8): a tile is GS heads x 128/GS positions
+// GS query heads per kv head (1, 2, 4, 8): a tile is GS heads x 128/GS positions; VD: width of a value head (64 or 32)
+template <int GS, bool POOLED, int VD>
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_pk,
@@ -91,7 +92,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             int nh, int nkv, int window, int pool, float scale, const float* __restrict__ head_scale,
                             const float* __restrict__ freq_v, int* __restrict__ status) {
   constexpr int HD = 64, PAGE = 64, TP = 128 / GS, NS = ATC_STAGES;
-  constexpr int Q_BYTES = 128 * HD * 2, KV_BYTES = PAGE * HD * 2;
+  constexpr int Q_BYTES = 128 * HD * 2, KV_BYTES = PAGE * HD * 2, V_BYTES = VD * PAGE * 2;
   extern __shared__ uint8_t atc_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)atc_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles want 1024
   uint8_t* sq = smem;
@@ -119,9 +120,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int h0 = kvh * GS;
   if (seq_slot[b] < 0) {   // a padding sequence: its rows are zero
     pdl_wait();
-    for (int idx = threadIdx.x; idx < rows * GS * (HD / 8); idx += blockDim.x) {
-      const int i = idx / (GS * (HD / 8)), rest = idx % (GS * (HD / 8));
-      reinterpret_cast<uint4*>(out + ((m_base + i) * nh + h0) * HD)[rest] = make_uint4(0, 0, 0, 0);
+    for (int idx = threadIdx.x; idx < rows * GS * (VD / 8); idx += blockDim.x) {
+      const int i = idx / (GS * (VD / 8)), rest = idx % (GS * (VD / 8));
+      reinterpret_cast<uint4*>(out + ((m_base + i) * nh + h0) * VD)[rest] = make_uint4(0, 0, 0, 0);
     }
     return;
   }
@@ -162,6 +163,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t t_o = tmem, t_s0 = tmem + 64, t_p0 = tmem + 192;   // O | S0 S1 | P0 P1 (columns)
   // instruction descriptor: float accumulate, bfloat16 operands, both K-major, N = 64, M = 128
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+  constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)VD >> 3) << 17) | ((128u >> 4) << 24);   // N = VD
   bool ok = true;
 
   if (warp == 4) {
@@ -182,8 +184,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const bool pooled = POOLED && i < npp;
         mbar_expect_tx(&k_full[s], KV_BYTES);
         tma_load_2d(sk + s * KV_BYTES, pooled ? &map_pk : &map_k, &k_full[s], 0, y);
-        mbar_expect_tx(&v_full[s], KV_BYTES);
-        tma_load_2d(sv + s * KV_BYTES, pooled ? &map_pv : &map_v, &v_full[s], 0, y);
+        mbar_expect_tx(&v_full[s], V_BYTES);
+        tma_load_2d(sv + s * V_BYTES, pooled ? &map_pv : &map_v, &v_full[s], 0, (page * nkv + kvh) * VD);
       }
     }
   } else if (warp == 5) {
@@ -208,19 +210,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!mbar_wait(&p_full[i & 1], (i >> 1) & 1, abort_flag)) { atomicExch(status, 14); ok = false; break; }
         if (!mbar_wait(&v_full[s], (i / NS) & 1, abort_flag)) { atomicExch(status, 15); ok = false; break; }
         tc_fence_after();
-        const uint32_t va = smem_u32(sv + s * KV_BYTES);
+        const uint32_t va = smem_u32(sv + s * V_BYTES);
         if (POOLED) {
           const uint32_t t_p = t_s0 + 64 * (i & 1);   // hi in the scores' first 32 columns, lo in the next 32
 #pragma unroll
           for (int kk = 0; kk < PAGE / 16; kk++)
-            umma_bf16_ts(t_o, t_p + kk * 8, make_desc(va + kk * 32), IDESC, (i > 0 || kk > 0));
+            umma_bf16_ts(t_o, t_p + kk * 8, make_desc(va + kk * 32), IDESC_PV, (i > 0 || kk > 0));
 #pragma unroll
           for (int kk = 0; kk < PAGE / 16; kk++)
-            umma_bf16_ts(t_o, t_p + 32 + kk * 8, make_desc(va + kk * 32), IDESC, 1);
+            umma_bf16_ts(t_o, t_p + 32 + kk * 8, make_desc(va + kk * 32), IDESC_PV, 1);
         } else {
 #pragma unroll
           for (int kk = 0; kk < PAGE / 16; kk++)
-            umma_bf16_ts(t_o, t_p0 + 32 * (i & 1) + kk * 8, make_desc(va + kk * 32), IDESC, (i > 0 || kk > 0));
+            umma_bf16_ts(t_o, t_p0 + 32 * (i & 1) + kk * 8, make_desc(va + kk * 32), IDESC_PV, (i > 0 || kk > 0));
         }
         umma_commit(&kv_empty[s]);
         umma_commit(&pv_done[i & 1]);
@@ -273,7 +275,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_fence_after();
         const float f = move ? ex2(m_used - m_new) : 1.f;
 #pragma unroll
-        for (int hcol = 0; hcol < HD; hcol += 32) {
+        for (int hcol = 0; hcol < VD; hcol += 32) {
           uint32_t o[32];
           tmem_ld32(t_o + lane_base + hcol, o);
           tmem_ld_wait();
@@ -316,8 +318,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // the page with the end of the sequence (or of the pooled blocks): its value columns beyond it become zero
         if (!mbar_wait(&v_full[s], (i / NS) & 1, abort_flag)) { atomicExch(status, 19); ok = false; break; }
         const int n_valid = key_end - key0;
-        if (r < HD) {
-          uint8_t* vrow = sv + s * KV_BYTES + r * 128;   // dimension r: 64 positions, 16-byte pieces swizzled by r & 7
+        if (r < VD) {
+          uint8_t* vrow = sv + s * V_BYTES + r * 128;   // dimension r: 64 positions, 16-byte pieces swizzled by r & 7
           for (int cc = n_valid / 8; cc < 8; cc++) {
             bf16* piece = reinterpret_cast<bf16*>(vrow + ((cc ^ (r & 7)) << 4));
             for (int e = max(0, n_valid - cc * 8); e < 8; e++) piece[e] = __float2bfloat16_rn(0.f);
@@ -336,28 +338,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_after();
       float inv = l > 0.f ? 1.0f / l : 0.f;
       if (gate && row_valid) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(m_base + pi) * gate_stride + h0 + g])));
-      uint4* orow = reinterpret_cast<uint4*>(out + ((m_base + pi) * nh + h0 + g) * HD);
-      uint32_t o[HD];
+      uint4* orow = reinterpret_cast<uint4*>(out + ((m_base + pi) * nh + h0 + g) * VD);
+      uint32_t o[VD];
       tmem_ld32(t_o + lane_base, o);
-      tmem_ld32(t_o + lane_base + 32, o + 32);
+      if (VD > 32) tmem_ld32(t_o + lane_base + 32, o + (VD > 32 ? 32 : 0));
       tmem_ld_wait();
       if (row_valid) {
 #pragma unroll
-        for (int c = 0; c < HD; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * inv);
+        for (int c = 0; c < VD; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * inv);
         if (POOLED && freq_v) {
-          // values were cached turned by their positions: the sum is turned back by the query's (pairs c, c + 32)
+          // values were cached turned by their positions: the sum is turned back by the query's (pairs c, c + VD/2)
           const float fpos = (float)qpos;
 #pragma unroll
-          for (int c = 0; c < HD / 2; c++) {
+          for (int c = 0; c < VD / 2; c++) {
             float sn, cs;
             sincosf(fpos * freq_v[c], &sn, &cs);
-            const float a = __uint_as_float(o[c]), bb = __uint_as_float(o[c + HD / 2]);
+            const float a = __uint_as_float(o[c]), bb = __uint_as_float(o[c + VD / 2]);
             o[c] = __float_as_uint(a * cs + bb * sn);
-            o[c + HD / 2] = __float_as_uint(bb * cs - a * sn);
+            o[c + VD / 2] = __float_as_uint(bb * cs - a * sn);
           }
         }
 #pragma unroll
-        for (int c = 0; c < HD; c += 8) {
+        for (int c = 0; c < VD; c += 8) {
           uint4 w;
           uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
@@ -381,7 +383,7 @@ LEB_API int leb_attention_prefill_tc_supported(int nh, int nkv, int hd, int page
   return G == 1 || G == 2 || G == 4 || G == 8;
 }
 
-template <bool POOLED>
+template <bool POOLED, int VD>
 static int launch_attention_prefill_tc(const char* who, void* out, const void* q, int q_stride, int M, const void* k_pool,
                                        const void* v_pool, int n_pages, const int* block_table, int bt_width,
                                        const void* pk_pool, const void* pv_pool, int n_pooled_pages, const int* pool_table,
@@ -402,26 +404,26 @@ static int launch_attention_prefill_tc(const char* who, void* out, const void* q
   CUtensorMap mq, mk, mv, mpk, mpv;
   if (tensor_map(&mq, q, M, nh * hd, q_stride, TP)) return 1;
   if (tensor_map(&mk, k_pool, n_pages * nkv * page_size, hd, hd, page_size)) return 1;
-  if (tensor_map(&mv, v_pool, n_pages * nkv * hd, page_size, page_size, hd)) return 1;
+  if (tensor_map(&mv, v_pool, n_pages * nkv * VD, page_size, page_size, VD)) return 1;
   if (pooled) {
     if (tensor_map(&mpk, pk_pool, n_pooled_pages * nkv * page_size, hd, hd, page_size)) return 1;
-    if (tensor_map(&mpv, pv_pool, n_pooled_pages * nkv * hd, page_size, page_size, hd)) return 1;
+    if (tensor_map(&mpv, pv_pool, n_pooled_pages * nkv * VD, page_size, page_size, VD)) return 1;
   } else {
     mpk = mk;
     mpv = mv;
   }
   dim3 grid(nkv, ceil_div(max_qlen, TP), B);
   LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "%s: grid too large", who);
-  const size_t smem = 1024 + 128 * 64 * 2 + 2 * ATC_STAGES * 64 * 64 * 2;
+  const size_t smem = 1024 + 128 * 64 * 2 + ATC_STAGES * (64 + VD) * 64 * 2;
 #define LEB_ATC(GS_)                                                                                              \
   {                                                                                                               \
     static bool set = false;                                                                                      \
     if (!set) {                                                                                                   \
-      if (cudaFuncSetAttribute(attention_prefill_tc_kernel<GS_, POOLED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      if (cudaFuncSetAttribute(attention_prefill_tc_kernel<GS_, POOLED, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return leb_fail("%s: %zu bytes of shared memory per block refused", who, smem);                         \
       set = true;                                                                                                 \
     }                                                                                                             \
-    leb_launch(attention_prefill_tc_kernel<GS_, POOLED>, grid, dim3(ATC_THREADS), smem, st,                       \
+    leb_launch(attention_prefill_tc_kernel<GS_, POOLED, VD>, grid, dim3(ATC_THREADS), smem, st,                       \
         mq, mk, mv, mpk, mpv, (bf16*)out, block_table, bt_width, pool_table, pt_width, seq_slot, seq_pos0, seq_qstart, \
         seq_qlen, (const bf16*)gate, gate_stride, nh, nkv, window, pooled ? pool : 0, scale, head_scale, freq_v, status); \
   }
@@ -446,7 +448,7 @@ LEB_API int leb_attention_prefill_tc(void* out, const void* q, int q_stride, int
                                      const int* seq_qlen, const void* gate, int gate_stride, int B, int nh, int nkv,
                                      int hd, int page_size, int window, float scale, int max_qlen, int* status,
                                      cudaStream_t st) {
-  return launch_attention_prefill_tc<false>("leb_attention_prefill_tc", out, q, q_stride, M, k_pool, v_pool, n_pages,
+  return launch_attention_prefill_tc<false, 64>("leb_attention_prefill_tc", out, q, q_stride, M, k_pool, v_pool, n_pages,
                                             block_table, bt_width, nullptr, nullptr, 0, nullptr, 0, seq_slot, seq_pos0,
                                             seq_qstart, seq_qlen, gate, gate_stride, B, nh, nkv, hd, page_size, window, 0,
                                             scale, nullptr, nullptr, max_qlen, status, st);
@@ -454,16 +456,23 @@ LEB_API int leb_attention_prefill_tc(void* out, const void* q, int q_stride, int
 
 // The same over a window with pooled blocks behind it (pool 0: none): pk_pool / pv_pool hold one row per
 // complete block in the layout of k_pool / v_pool, pool_table [B][pt_width] their page lists; scores times
-// head_scale[h]; freq_v [32] or null: the result of a row is turned back by its position (pairs c, c + 32).
+// head_scale[h]; v_pool / pv_pool [pages][nkv][vd][64] with vd 64 or 32, out [M, nh*vd]; freq_v [vd/2] or null: the
+// result of a row is turned back by its position (pairs c, c + vd/2).
 LEB_API int leb_attention_pooled_tc(void* out, const void* q, int q_stride, int M, const void* k_pool, const void* v_pool,
                                     int n_pages, const int* block_table, int bt_width, const void* pk_pool,
                                     const void* pv_pool, int n_pooled_pages, const int* pool_table, int pt_width,
                                     const int* seq_slot, const int* seq_pos0, const int* seq_qstart, const int* seq_qlen,
-                                    const float* head_scale, const float* freq_v, int B, int nh, int nkv, int hd,
+                                    const float* head_scale, const float* freq_v, int B, int nh, int nkv, int hd, int vd,
                                     int page_size, int window, int pool, int max_qlen, int* status, cudaStream_t st) {
   LEB_REQUIRE(head_scale != nullptr, "leb_attention_pooled_tc: a factor per head is required");
-  return launch_attention_prefill_tc<true>("leb_attention_pooled_tc", out, q, q_stride, M, k_pool, v_pool, n_pages,
-                                           block_table, bt_width, pk_pool, pv_pool, n_pooled_pages, pool_table, pt_width,
-                                           seq_slot, seq_pos0, seq_qstart, seq_qlen, nullptr, 0, B, nh, nkv, hd, page_size,
-                                           window, pool, 1.0f, head_scale, freq_v, max_qlen, status, st);
+  LEB_REQUIRE(vd == 64 || vd == 32, "leb_attention_pooled_tc: value heads of %d numbers (64 or 32)", vd);
+#define LEB_APT_ARGS "leb_attention_pooled_tc", out, q, q_stride, M, k_pool, v_pool, n_pages, block_table, bt_width, pk_pool, \
+                     pv_pool, n_pooled_pages, pool_table, pt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen, nullptr, 0, B, nh, \
+                     nkv, hd, page_size, window, pool, 1.0f, head_scale, freq_v, max_qlen, status, st
+  const int rc = vd == 64 ? launch_attention_prefill_tc<true, 64>(LEB_APT_ARGS) : launch_attention_prefill_tc<true, 32>(LEB_APT_ARGS);
+#undef LEB_APT_ARGS
+  return rc;
 }
+
+// Value widths the pooled entry point takes beside the sizes leb_attention_prefill_tc_supported names.
+LEB_API int leb_attention_pooled_tc_value_dim(int vd) { return vd == 64 || vd == 32; }

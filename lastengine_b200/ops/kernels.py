@@ -140,7 +140,8 @@ def _declare(L) -> None:
         "leb_attention_prefill_supported": [I, I, I, I],
         "leb_attention_prefill_tc_supported": [I, I, I, I],
         "leb_attention_prefill_tc": [P, P, I, I, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
-        "leb_attention_pooled_tc": [P, P, I, I, P, P, I, P, I, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P],
+        "leb_attention_pooled_tc": [P, P, I, I, P, P, I, P, I, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+        "leb_attention_pooled_tc_value_dim": [I],
         "leb_attention_prefill": [P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_gemm_bf16_skinny_slices": [I, I],
         "leb_gemm_bf16_skinny_supported": [P, P, I, I, I],
@@ -527,15 +528,16 @@ def attention_pooled(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v
         if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"attention_pooled: {n_splits} splits need {need} floats of scratch")
     L = lib()
-    if (out.dtype == torch.bfloat16 and n_splits == 1 and hd == vd and batch.max_qlen >= TC_ATTENTION_MIN_ROWS
-            and q.stride(0) % 8 == 0 and L.leb_attention_prefill_tc_supported(nh, nkv, hd, page_size)):
+    if (out.dtype == torch.bfloat16 and n_splits == 1 and batch.max_qlen >= TC_ATTENTION_MIN_ROWS
+            and q.stride(0) % 8 == 0 and L.leb_attention_prefill_tc_supported(nh, nkv, hd, page_size)
+            and L.leb_attention_pooled_tc_value_dim(vd)):
         # prompts at the tensor-core kernel's sizes: pooled pages ahead of the window's, weights as two bfloat16 terms
         _check(L.leb_attention_pooled_tc(
             _ptr(out), _ptr(q), q.stride(0), M, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
             block_table.shape[1], _ptr(pk_pool) if pool > 0 else None, _ptr(pv_pool) if pool > 0 else None,
             pk_pool.shape[0] if pool > 0 else 0, _ptr(pool_table) if pool > 0 else None, pt_width, _ptr(batch.seq_slot),
             _ptr(batch.seq_pos0), _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(head_scale), _ptr(freq_v),
-            batch.n_seqs, nh, nkv, hd, page_size, int(window), int(pool), batch.max_qlen,
+            batch.n_seqs, nh, nkv, hd, vd, page_size, int(window), int(pool), batch.max_qlen,
             _ptr(_status_word(out.device)), _stream()))
         return
     single = batch.max_qlen == 1 and M == batch.n_seqs

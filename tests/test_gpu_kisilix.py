@@ -281,20 +281,23 @@ def test_attention_alone_whole_in_portions_and_batched(heads, kv, dim, vdim, sca
                                [0, 1, 3, 4, 10, 12, 30], dtype)
 
 
-ATT_TENSOR_CORE_CASES = [  # the sizes the tensor-core prompt kernel takes (heads of 64, 1/2/4/8 query heads per kv head)
-    (8, 2, 0.13, 64, 1e4, 96, 4),        # 151 pooled blocks at the end of 700 rows: three pages of them
-    (8, 1, 0.1, 32, 5e5, 64, 64),        # window and block of a cache page
-    (4, 2, 0.2, 64, 1e3, 200, 7),        # a block that divides neither the window nor a page
-    (3, 3, 0.125, 0, 2e4, 33, 1),        # blocks of one position: every earlier position is seen, 667 pooled rows
+ATT_TENSOR_CORE_CASES = [  # sizes the tensor-core prompt kernel takes: key heads of 64, 1/2/4/8 query heads per kv head
+    # heads, kv heads, vdim, scale, rot dims, base, window, block
+    (8, 2, 64, 0.13, 64, 1e4, 96, 4),        # 151 pooled blocks at the end of 700 rows: three pages of them
+    (8, 1, 64, 0.1, 32, 5e5, 64, 64),        # window and block of a cache page
+    (4, 2, 64, 0.2, 64, 1e3, 200, 7),        # a block that divides neither the window nor a page
+    (3, 3, 64, 0.125, 0, 2e4, 33, 1),        # blocks of one position: every earlier position is seen, 667 pooled rows
+    (4, 1, 32, 0.15, 64, 1e4, 130, 5),       # value heads half as wide as the key heads
+    (2, 2, 32, 0.11, 16, 3e4, 64, 16),
 ]
 
 
-@pytest.mark.parametrize("heads,kv,scale,rot,base,size,pool", ATT_TENSOR_CORE_CASES)
-def test_attention_on_the_tensor_cores_whole_in_portions_and_batched(heads, kv, scale, rot, base, size, pool):
+@pytest.mark.parametrize("heads,kv,vdim,scale,rot,base,size,pool", ATT_TENSOR_CORE_CASES)
+def test_attention_on_the_tensor_cores_whole_in_portions_and_batched(heads, kv, vdim, scale, rot, base, size, pool):
     D = 64
-    rig = MixerRig("pooled_window_attention", att_params(D, heads, kv, 64, 64, scale, rot, base, size, pool), "bfloat16",
+    rig = MixerRig("pooled_window_attention", att_params(D, heads, kv, 64, vdim, scale, rot, base, size, pool), "bfloat16",
                    seed=11, max_tokens=4096)
-    m = att(heads, kv, 64, 64, scale, rot, base, size, pool)
+    m = att(heads, kv, 64, vdim, scale, rot, base, size, pool)
     whole_portions_and_batches(rig, lambda h: P.pooled_window_attention(h, rig.plain, m, 1e-5), (700, 9, 130), 40,
                                [0, 8, 9, 17, 40], "bfloat16")
 
