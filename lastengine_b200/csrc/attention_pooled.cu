@@ -201,8 +201,10 @@ __device__ __forceinline__ int blocks_seen(int qpos, int window, int pool) {
   return (window > 0 && pool > 0 && past > 0) ? past / pool : 0;
 }
 
+// Value heads up to 64 wide keep four blocks on an SM (128 registers a thread): the grids of a decode step are
+// sized for that many, and a block more than fit costs a second round.
 template <typename T, typename CT, int HDL>
-__global__ void __launch_bounds__(32 * PAT_WARPS)
+__global__ void __launch_bounds__(32 * PAT_WARPS, HDL <= 2 ? 4 : 1)
 attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restrict__ q,
                         const CT* __restrict__ k_pool, const CT* __restrict__ v_pool, const int* __restrict__ block_table,
                         int bt_width, const CT* __restrict__ pk_pool, const CT* __restrict__ pv_pool,
@@ -210,7 +212,7 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
                         const int* __restrict__ seq_pos0, const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
                         const float* __restrict__ head_scale, const float* __restrict__ freq_v, int nh, int nkv, int hd,
                         int vd, int page_size, int window, int pool, int QT, int HC, int n_splits) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int G = nh / nkv;
@@ -226,12 +228,14 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
   const int q0 = seq_qstart[b];
   const int pos0 = seq_pos0[b];
   const int R = QT * HC;
-  const int KS = hd + 1;
+  const int KS = ((hd + 3) & ~3) + 4;      // a key's row: 16-byte pieces, and eight lanes' pieces fall in 32 different banks
+  constexpr int VS = 36;                    // a value dimension's row of 32 positions, likewise
+  const bool hd4 = hd % 4 == 0;
 
   float* q_s = sm;                 // [R][hd]
-  float* k_s = q_s + R * hd;       // [32][hd + 1]
-  float* v_s = k_s + 32 * KS;      // [vd][33]: a dimension's 32 positions of the tile
-  float* p_s = v_s + 33 * vd;      // [PAT_WARPS][32]
+  float* k_s = q_s + ((R * hd + 3) & ~3);   // [32][KS], on 16 bytes like everything behind it
+  float* v_s = k_s + 32 * KS;      // [vd][VS]: a dimension's 32 positions of the tile
+  float* p_s = v_s + VS * vd;      // [PAT_WARPS][32]
   float* o_s = p_s + PAT_WARPS * 32;   // [PAT_WARPS][vd]
 
   if (slot < 0) {  // padding sequence: defined output, no cache access
@@ -282,66 +286,95 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
     for (int jj = 0; jj < HDL; jj++) acc[ri][jj] = 0.f;
   }
 
+  constexpr int EV = 16 / (int)sizeof(CT);      // cached numbers in a 16-byte load
+  // A tile's keys are one contiguous run and a dimension's 32 values another, so 16-byte loads bring a tile in.
+  // When two of each kind per thread cover a tile, the next tile's loads are issued before this tile is
+  // computed and stored to shared memory after it: the walk over the tiles does not wait on global memory.
+  const int nvk = 32 * hd / EV, nvv = vd * (32 / EV);
+  const bool vec = hd % EV == 0;
+  const bool ahead = vec && max(nvk, nvv) <= 2 * (int)blockDim.x;
+  struct Tile { bool pooled; int key0, limit, page; const CT *kp, *vp; size_t base, vbase; };
+  auto tile_of = [&](int ut) {
+    Tile t;
+    t.pooled = ut < np_tiles;
+    t.key0 = t.pooled ? ut * 32 : (tile_first + ut - np_tiles) * 32;
+    t.limit = t.pooled ? nb_hi : kv_len;          // rows beyond it hold stale bits
+    t.page = t.pooled ? pool_table[(size_t)b * pt_width + t.key0 / page_size]
+                      : block_table[(size_t)b * bt_width + t.key0 / page_size];
+    t.kp = t.pooled ? pk_pool : k_pool;
+    t.vp = t.pooled ? pv_pool : v_pool;
+    t.base = (((size_t)(t.page < 0 ? 0 : t.page) * nkv + kvh) * page_size + t.key0 % page_size) * hd;
+    t.vbase = ((size_t)(t.page < 0 ? 0 : t.page) * nkv + kvh) * vd * page_size + t.key0 % page_size;
+    return t;
+  };
+  auto load16 = [&](const Tile& t, int i0, uint4* rk, uint4* rv) {
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const int idx = i0 + u * blockDim.x + threadIdx.x;
+      rk[u] = make_uint4(0, 0, 0, 0);
+      rv[u] = make_uint4(0, 0, 0, 0);
+      if (t.page >= 0 && idx < nvk && t.key0 + idx * EV / hd < t.limit)
+        rk[u] = *reinterpret_cast<const uint4*>(t.kp + t.base + (size_t)idx * EV);
+      if (t.page >= 0 && idx < nvv)
+        rv[u] = *reinterpret_cast<const uint4*>(t.vp + t.vbase + (size_t)(idx / (32 / EV)) * page_size + (idx % (32 / EV)) * EV);
+    }
+  };
+  auto store16 = [&](const Tile& t, int i0, const uint4* rk, const uint4* rv) {
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const int idx = i0 + u * blockDim.x + threadIdx.x;
+      if (idx < nvk) {
+        const int kk = idx * EV / hd, d = idx * EV - kk * hd;
+        const CT* el = reinterpret_cast<const CT*>(&rk[u]);
+#pragma unroll
+        for (int j = 0; j < EV; j++) k_s[kk * KS + d + j] = to_f32(el[j]);
+      }
+      if (idx < nvv) {
+        const int d = idx / (32 / EV), k0 = (idx % (32 / EV)) * EV;
+        const CT* el = reinterpret_cast<const CT*>(&rv[u]);
+#pragma unroll
+        for (int j = 0; j < EV; j++) v_s[d * VS + k0 + j] = (t.key0 + k0 + j < t.limit) ? to_f32(el[j]) : 0.f;
+      }
+    }
+  };
+  uint4 nk[2], nv[2];      // the tile ahead
+  Tile tnext;
+  if (ahead && t_lo < t_hi) {
+    tnext = tile_of(t_lo);
+    load16(tnext, 0, nk, nv);
+  }
   for (int ut = t_lo; ut < t_hi; ut++) {
-    const bool pooled = ut < np_tiles;
-    const int key0 = pooled ? ut * 32 : (tile_first + ut - np_tiles) * 32;
-    const int limit = pooled ? nb_hi : kv_len;          // rows beyond it hold stale bits
-    const int page = pooled ? pool_table[(size_t)b * pt_width + key0 / page_size]
-                            : block_table[(size_t)b * bt_width + key0 / page_size];
-    const CT* kp = pooled ? pk_pool : k_pool;
-    const CT* vp = pooled ? pv_pool : v_pool;
-    const size_t base = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * page_size + key0 % page_size) * hd;
-    const size_t vbase = ((size_t)(page < 0 ? 0 : page) * nkv + kvh) * vd * page_size + key0 % page_size;
+    const Tile tl = ahead ? tnext : tile_of(ut);
+    const bool pooled = tl.pooled;
+    const int key0 = tl.key0;
     __syncthreads();
-    constexpr int EV = 16 / (int)sizeof(CT);      // cached numbers in a 16-byte load
-    if (hd % EV == 0) {
-      // the tile's keys are one contiguous run, a dimension's 32 values another: 16-byte loads, two of each
-      // kind in flight per thread before anything is stored
-      const int nvk = 32 * hd / EV, nvv = vd * (32 / EV);
+    if (ahead) {
+      store16(tl, 0, nk, nv);
+    } else if (vec) {
       for (int i0 = 0; i0 < max(nvk, nvv); i0 += 2 * blockDim.x) {
         uint4 rk[2], rv[2];
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int idx = i0 + u * blockDim.x + threadIdx.x;
-          rk[u] = make_uint4(0, 0, 0, 0);
-          rv[u] = make_uint4(0, 0, 0, 0);
-          if (page >= 0 && idx < nvk && key0 + idx * EV / hd < limit)
-            rk[u] = *reinterpret_cast<const uint4*>(kp + base + (size_t)idx * EV);
-          if (page >= 0 && idx < nvv)
-            rv[u] = *reinterpret_cast<const uint4*>(vp + vbase + (size_t)(idx / (32 / EV)) * page_size + (idx % (32 / EV)) * EV);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int idx = i0 + u * blockDim.x + threadIdx.x;
-          if (idx < nvk) {
-            const int kk = idx * EV / hd, d = idx * EV - kk * hd;
-            const CT* el = reinterpret_cast<const CT*>(&rk[u]);
-#pragma unroll
-            for (int j = 0; j < EV; j++) k_s[kk * KS + d + j] = to_f32(el[j]);
-          }
-          if (idx < nvv) {
-            const int d = idx / (32 / EV), k0 = (idx % (32 / EV)) * EV;
-            const CT* el = reinterpret_cast<const CT*>(&rv[u]);
-#pragma unroll
-            for (int j = 0; j < EV; j++) v_s[d * 33 + k0 + j] = (key0 + k0 + j < limit) ? to_f32(el[j]) : 0.f;
-          }
-        }
+        load16(tl, i0, rk, rv);
+        store16(tl, i0, rk, rv);
       }
     } else {
       for (int idx = threadIdx.x; idx < 32 * hd; idx += blockDim.x) {
         const int kk = idx / hd, d = idx - kk * hd;
         float kv = 0.f;
-        if (page >= 0 && key0 + kk < limit) kv = to_f32(kp[base + idx]);
+        if (tl.page >= 0 && key0 + kk < tl.limit) kv = to_f32(tl.kp[tl.base + idx]);
         k_s[kk * KS + d] = kv;
       }
       for (int idx = threadIdx.x; idx < 32 * vd; idx += blockDim.x) {
         const int d = idx / 32, kk = idx - d * 32;
         float vv = 0.f;
-        if (page >= 0 && key0 + kk < limit) vv = to_f32(vp[vbase + (size_t)d * page_size + kk]);
-        v_s[d * 33 + kk] = vv;
+        if (tl.page >= 0 && key0 + kk < tl.limit) vv = to_f32(tl.vp[tl.vbase + (size_t)d * page_size + kk]);
+        v_s[d * VS + kk] = vv;
       }
     }
     __syncthreads();
+    if (ahead && ut + 1 < t_hi) {
+      tnext = tile_of(ut + 1);
+      load16(tnext, 0, nk, nv);
+    }
 #pragma unroll
     for (int ri = 0; ri < PAT_RPW; ri++) {
       const int r = warp + ri * PAT_WARPS;
@@ -353,7 +386,23 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
       const float* qv = q_s + r * hd;
       const float* kr = k_s + lane * KS;
       float s = 0.f;
-      for (int d = 0; d < hd; d++) s += qv[d] * kr[d];
+      if (hd4) {
+        const float4* q4 = reinterpret_cast<const float4*>(qv);
+        const float4* k4 = reinterpret_cast<const float4*>(kr);
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int d = 0; d < hd / 4; d++) {
+          const float4 a = q4[d], c = k4[d];
+          s4[0] = fmaf(a.x, c.x, s4[0]);
+          s4[1] = fmaf(a.y, c.y, s4[1]);
+          s4[2] = fmaf(a.z, c.z, s4[2]);
+          s4[3] = fmaf(a.w, c.w, s4[3]);
+        }
+        s = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      } else {
+#pragma unroll 8
+        for (int d = 0; d < hd; d++) s += qv[d] * kr[d];
+      }
       s *= head_scale[h];
       const int kp_ = key0 + lane;
       const bool valid = pooled ? kp_ < blocks_seen(qpos, window, pool)
@@ -370,10 +419,18 @@ attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* 
       for (int jj = 0; jj < HDL; jj++) {
         const int d = lane + 32 * jj;
         if (d < vd) {
-          float a = 0.f;
-#pragma unroll 8
-          for (int kk = 0; kk < 32; kk++) a += p_s[warp * 32 + kk] * v_s[d * 33 + kk];
-          acc[ri][jj] = acc[ri][jj] * corr + a;
+          const float4* p4 = reinterpret_cast<const float4*>(p_s + warp * 32);
+          const float4* v4 = reinterpret_cast<const float4*>(v_s + d * VS);
+          float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {
+            const float4 pw = p4[kk], vv = v4[kk];
+            a4[0] = fmaf(pw.x, vv.x, a4[0]);
+            a4[1] = fmaf(pw.y, vv.y, a4[1]);
+            a4[2] = fmaf(pw.z, vv.z, a4[2]);
+            a4[3] = fmaf(pw.w, vv.w, a4[3]);
+          }
+          acc[ri][jj] = acc[ri][jj] * corr + ((a4[0] + a4[1]) + (a4[2] + a4[3]));
         }
       }
       __syncwarp();
@@ -473,7 +530,7 @@ static int launch_attention_pooled(void* out, float* part, const void* q, const 
   if (QT > max_qlen) QT = max_qlen;
   const int R = QT * HC;
   const int n_hc = ceil_div(G, HC);
-  const size_t smem = ((size_t)R * hd + 32 * (hd + 1) + 33 * vd + PAT_WARPS * 32 + PAT_WARPS * vd) * sizeof(float);
+  const size_t smem = ((size_t)((R * hd + 3) & ~3) + 32 * (((hd + 3) & ~3) + 4) + 36 * vd + PAT_WARPS * 32 + PAT_WARPS * vd) * sizeof(float);
   auto kern = attention_pooled_kernel<T, CT, HDL>;
   static size_t smem_set = 0;
   if (smem > 48 * 1024 && smem > smem_set) {
