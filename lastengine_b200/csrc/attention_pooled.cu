@@ -202,7 +202,7 @@ __device__ __forceinline__ int blocks_seen(int qpos, int window, int pool) {
 }
 
 // Value heads up to 64 wide keep four blocks on an SM (128 registers a thread): the grids of a decode step are
-// sized for that many, and a block more than fit costs a second round.
+// sized for that many, and a block more than fit waits for a place.
 template <typename T, typename CT, int HDL>
 __global__ void __launch_bounds__(32 * PAT_WARPS, HDL <= 2 ? 4 : 1)
 attention_pooled_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restrict__ q,
