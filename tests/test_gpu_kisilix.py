@@ -730,3 +730,34 @@ def test_replay_program_with_a_cache_sized_to_the_tokens_alone(dirs, tmp_path):
         assert at == lg.shape[0]
     for r, t in reqs.items():
         assert close(np.concatenate(got[r]), plain(name, dirs, t), "float32"), r
+
+
+def test_command_line_generates_samples_and_compares_the_two_number_formats(dirs):
+    """bin/lastengine on a folder of this design: greedy and sampled generation (the same seed gives the same
+    tokens), the dump of a greedy run, and bfloat16 against the 32-bit path step by step."""
+    import json
+    import subprocess
+    import sys
+    exe = os.path.join(H.ROOT, "bin", "lastengine")
+    d = dirs["A"]
+    base = [sys.executable, exe, "generate", "--model", d, "--prompt-ids", "1,2,3", "--prompt-ids", "9 8 7 6 5", "--max-new-tokens", "6",
+            "--stop-token-id", "199"]
+    p = subprocess.run(base + ["--dtype", "float32", "--temperature", "0"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-1500:]
+    rows = [json.loads(l) for l in p.stdout.splitlines()]
+    assert len(rows) == 2 and all(1 <= len(r["tokens"]) <= 6 for r in rows)
+    want, margins = plain_greedy("A", dirs, [1, 2, 3], 1)
+    if margins[0] > 1e-4:
+        assert rows[0]["tokens"][0] == want[0]
+    sampled = [subprocess.run(base + ["--temperature", "0.9", "--top-k", "20", "--seed", "5"], capture_output=True, text=True, timeout=600)
+               for _ in range(2)]
+    assert sampled[0].returncode == 0, sampled[0].stderr[-1500:]
+    assert sampled[0].stdout == sampled[1].stdout
+    p2 = subprocess.run([sys.executable, exe, "tf-dump", d, "1,2,3", "6", "--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert p2.returncode == 0, p2.stderr[-1500:]
+    dump = json.loads(p2.stdout.splitlines()[-1])
+    if len(rows[0]["tokens"]) == 6:
+        assert dump["gen_ids"] == rows[0]["tokens"]
+    p3 = subprocess.run([sys.executable, exe, "dense-cmp", d, "1,2,3", "6"], capture_output=True, text=True, timeout=600)
+    assert p3.returncode == 0, p3.stderr[-1500:]
+    assert "/6 argmax agree, mean |dlogprob|" in p3.stdout.splitlines()[-1]
