@@ -421,12 +421,48 @@ LEB_API int leb_group_norm_gate(void* out, int dtype, const float* y, const floa
 template <typename TH>
 __global__ void __launch_bounds__(512)
 postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ w,
-                         const float* __restrict__ bias, float eps, TH* __restrict__ h, int D) {
-  extern __shared__ float row[];
+                         const float* __restrict__ bias, float eps, TH* __restrict__ h, int D, int vec) {
+  extern __shared__ __align__(16) float row[];
   __shared__ float red[33];
   pdl_wait();
   const size_t m = blockIdx.x;
   float s = 0.f;
+  if (vec) {      // D is a multiple of four and the rows start on 16 bytes: four numbers a load and a store
+    const float4* x4 = reinterpret_cast<const float4*>(x + m * D);
+    const float4* y4 = reinterpret_cast<const float4*>(y + m * D);
+    float4* row4 = reinterpret_cast<float4*>(row);
+    for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+      const float4 a = x4[i], c = y4[i];
+      const float4 t = make_float4(alpha * a.x + c.x, alpha * a.y + c.y, alpha * a.z + c.z, alpha * a.w + c.w);
+      row4[i] = t;
+      s += (t.x + t.y) + (t.z + t.w);
+    }
+    const float mean = block_sum(s, red) / (float)D;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+      const float4 t = row4[i];
+      const float d0 = t.x - mean, d1 = t.y - mean, d2 = t.z - mean, d3 = t.w - mean;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+    const float r = 1.0f / sqrtf(block_sum(q, red) / (float)D + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+    float4* xo = reinterpret_cast<float4*>(x + m * D);
+    for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+      const float4 t = row4[i], ww = w4[i], bb = bias ? b4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 o = make_float4((t.x - mean) * r * ww.x + bb.x, (t.y - mean) * r * ww.y + bb.y,
+                                   (t.z - mean) * r * ww.z + bb.z, (t.w - mean) * r * ww.w + bb.w);
+      xo[i] = o;
+      if (h) {
+        TH* hp = h + m * D + 4 * (size_t)i;
+        hp[0] = from_f32<TH>(o.x);
+        hp[1] = from_f32<TH>(o.y);
+        hp[2] = from_f32<TH>(o.z);
+        hp[3] = from_f32<TH>(o.w);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     const float t = alpha * x[m * D + i] + y[m * D + i];
     row[i] = t;
@@ -452,6 +488,7 @@ LEB_API int leb_postnorm_residual(float* x, const float* y, float alpha, const f
   LEB_REQUIRE((size_t)D * sizeof(float) <= 160 * 1024, "leb_postnorm_residual: a width of %d does not fit shared memory", D);
   const size_t smem = (size_t)D * sizeof(float);
   const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+  const int vec = D % 4 == 0 && ((((uintptr_t)x | (uintptr_t)y | (uintptr_t)w | (uintptr_t)bias) & 15) == 0);
   LebPlainLaunches plain(true);
   static bool set = false;
   if (smem > 48 * 1024 && !set) {
@@ -460,9 +497,9 @@ LEB_API int leb_postnorm_residual(float* x, const float* y, float alpha, const f
     set = true;
   }
   if (!h || h_dtype == LEB_F32)
-    leb_launch(postnorm_residual_kernel<float>, dim3(M), dim3(threads), smem, st, x, y, alpha, w, bias, eps, (float*)h, D);
+    leb_launch(postnorm_residual_kernel<float>, dim3(M), dim3(threads), smem, st, x, y, alpha, w, bias, eps, (float*)h, D, vec);
   else if (h_dtype == LEB_BF16)
-    leb_launch(postnorm_residual_kernel<bf16>, dim3(M), dim3(threads), smem, st, x, y, alpha, w, bias, eps, (bf16*)h, D);
+    leb_launch(postnorm_residual_kernel<bf16>, dim3(M), dim3(threads), smem, st, x, y, alpha, w, bias, eps, (bf16*)h, D, vec);
   else
     return leb_fail("leb_postnorm_residual: unknown dtype %d", h_dtype);
   LEB_CHECK_LAUNCH("leb_postnorm_residual");

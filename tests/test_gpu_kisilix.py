@@ -488,7 +488,7 @@ def test_an_excluded_group_loses_to_a_negative_choice_score():
     assert err(rig.run(h), P.expert_mixture(h, rig.plain, f)) < H.TOL_F32
 
 
-@pytest.mark.parametrize("D", [40, 64, 256, 1000])
+@pytest.mark.parametrize("D", [40, 42, 64, 256, 1000, 2048])
 @pytest.mark.parametrize("alpha", [1.0, 2.5])
 def test_sum_and_layer_norm_with_bias(D, alpha):
     rng = np.random.default_rng(D)
