@@ -1,2 +1,2 @@
 """Architectures the library knows.  Importing registers them."""
-from . import kisilix, lenesun, lfm3, zekivik  # noqa: F401
+from . import kisilix, lenesun, lfm3, tevilix, zekivik  # noqa: F401

@@ -1,0 +1,430 @@
+// Softmax attention whose scores are mixed across the heads before the softmax ("talking heads"):
+//     s_g(i, j) = scale * q_g(i) . k_kv(g)(j)                for every query head g
+//     t_h(i, j) = sum_g talk[h, g] * s_g(i, j)               mixed with a learned [H, H] matrix
+//     p_h(i, :) = softmax over the visible j of t_h(i, :)    j <= i, and i - j < window when there is a window
+//     o_h(i)    = sum_j p_h(i, j) * v_kv(h)(j)               (then times sigmoid(gate) where a gate is given)
+// over the paged cache (keys [page][kv head][position][dim], values [page][kv head][dim][position]).
+//
+// A head's weights depend on every head's scores, so a block takes ALL heads of a few query rows of one
+// sequence and walks the key range in tiles: the tile's keys and values of every kv head go to shared memory,
+// each warp forms the raw scores of its (row, head) pairs with a lane per key, the pairs' scores meet in
+// shared memory, each warp mixes, masks and runs the streaming softmax for its pairs (lane = key), and adds
+// the weighted values with a lane per value dimension.  Scores, mixing, softmax and sums are float whatever
+// the cache holds.  The same kernel serves prompts, portions and decode steps; a decode step may cut the key
+// range over several blocks (partial maximum, sum and values to scratch, merged by a second kernel).
+#include "common.cuh"
+
+#define AMX_NEG (-1e30f)
+constexpr int AMX_MAX_WARPS = 16;
+
+template <typename T> struct AmxPiece;      // a 16-byte piece of a cached row as floats
+template <> struct AmxPiece<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+};
+template <> struct AmxPiece<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const bf16* p, float* f) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+// Shared memory, in this order: talk [H*H] | q [NP][hdp] | raw [NP][KT] | p [NP][KT] (floats), then
+// keys [G][KT][KS] and values [G][KT][vdp] in the cache's type.  NP = QT * H pairs; pair = row * H + head.
+template <typename T, int HDL, int RPW>
+__global__ void __launch_bounds__(32 * AMX_MAX_WARPS)
+attention_mixed_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restrict__ q, int ldq,
+                       const T* __restrict__ k_pool, const T* __restrict__ v_pool, const int* __restrict__ block_table,
+                       int bt_width, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
+                       const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen, const float* __restrict__ talk,
+                       const float* __restrict__ gate, int ldg, int H, int G, int hd, int vd, int page_size, int window,
+                       float scale, int QT, int KT, int n_splits) {
+  extern __shared__ __align__(16) unsigned char amx_sm[];
+  constexpr int EV = AmxPiece<T>::N;
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int b = blockIdx.z, split = blockIdx.y;
+  const int slot = seq_slot[b];
+  const int qlen = seq_qlen ? seq_qlen[b] : 1;
+  const int row_lo = blockIdx.x * QT;
+  if (row_lo >= qlen) return;
+  const int nrows = min(QT, qlen - row_lo);
+  const int q0 = seq_qstart[b], pos0 = seq_pos0[b];
+  const int Gq = H / G;
+  const int NP = QT * H;
+  const int hdp = (hd + 7) & ~7, KS = hdp + EV, vdp = (vd + 7) & ~7;
+
+  float* talk_s = reinterpret_cast<float*>(amx_sm);
+  float* q_s = talk_s + ((H * H + 3) & ~3);
+  float* raw_s = q_s + (size_t)NP * hdp;
+  float* p_s = raw_s + (size_t)NP * KT;
+  T* k_s = reinterpret_cast<T*>(p_s + (size_t)NP * KT);
+  T* v_s = k_s + (size_t)G * KT * KS;
+
+  // this warp's pairs: warp + nw * r
+  int pr_i[RPW], pr_h[RPW], pr_c[RPW];
+  bool pr_on[RPW];
+  bool same_c = true;
+#pragma unroll
+  for (int r = 0; r < RPW; r++) {
+    const int p = warp + nw * r;
+    pr_i[r] = p / H;
+    pr_h[r] = p - pr_i[r] * H;
+    pr_c[r] = pr_h[r] / Gq;
+    pr_on[r] = p < NP && pr_i[r] < nrows;
+    if (p >= NP) { pr_i[r] = 0; pr_h[r] = 0; pr_c[r] = 0; }
+    if (pr_c[r] != pr_c[0]) same_c = false;
+  }
+
+  if (slot < 0) {      // a padding sequence: a defined result, no cache access
+#pragma unroll
+    for (int r = 0; r < RPW; r++) {
+      if (!pr_on[r]) continue;
+      const size_t m = (size_t)q0 + row_lo + pr_i[r];
+      if (n_splits == 1) {
+        for (int d = lane; d < vd; d += 32) out[(m * H + pr_h[r]) * vd + d] = from_f32<T>(0.f);
+      } else {
+        float* pp = part + ((m * H + pr_h[r]) * n_splits + split) * (size_t)(vd + 2);
+        if (lane == 0) { pp[0] = AMX_NEG; pp[1] = 0.f; }
+        for (int d = lane; d < vd; d += 32) pp[2 + d] = 0.f;
+      }
+    }
+    return;
+  }
+
+  for (int idx = threadIdx.x; idx < H * H; idx += blockDim.x) talk_s[idx] = talk[idx];
+  for (int idx = threadIdx.x; idx < NP * hdp; idx += blockDim.x) {
+    const int p = idx / hdp, d = idx - p * hdp;
+    const int i = p / H, h = p - i * H;
+    float v = 0.f;
+    if (i < nrows && d < hd) v = to_f32(q[(size_t)(q0 + row_lo + i) * ldq + (size_t)h * hd + d]);
+    q_s[idx] = v;
+  }
+
+  const int kv_len = pos0 + qlen;
+  const int pos_lo = pos0 + row_lo, pos_hi = pos_lo + nrows - 1;
+  const int key_lo = (window > 0 && pos_lo + 1 > window) ? pos_lo + 1 - window : 0;
+  const int tile_first = key_lo / KT, n_tiles = pos_hi / KT - tile_first + 1;
+  const int per_split = (n_tiles + n_splits - 1) / n_splits;
+  const int t_lo = split * per_split, t_hi = min(n_tiles, t_lo + per_split);
+
+  float mx[RPW], l[RPW], acc[RPW][HDL];
+#pragma unroll
+  for (int r = 0; r < RPW; r++) {
+    mx[r] = AMX_NEG;
+    l[r] = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < HDL; jj++) acc[r][jj] = 0.f;
+  }
+  const bool kvec = hd % EV == 0;
+  const int jc = lane < KT ? lane : KT - 1;      // lanes beyond the tile's keys compute on its last key and are ignored
+
+  for (int ut = t_lo; ut < t_hi; ut++) {
+    const int key0 = (tile_first + ut) * KT;
+    const int page = block_table[(size_t)b * bt_width + key0 / page_size];
+    const int in_page = key0 % page_size;
+    __syncthreads();      // the tile before is used up (and q, talk are in place)
+    // keys: [c][j][0..hdp) with zeros behind hd and for positions that hold nothing yet
+    if (kvec) {
+      const int per_row = hdp / EV, total = G * KT * per_row;
+      for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int c = idx / (KT * per_row), rest = idx - c * (KT * per_row);
+        const int j = rest / per_row, d0 = (rest - j * per_row) * EV;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (page >= 0 && key0 + j < kv_len && d0 < hd)
+          v = *reinterpret_cast<const uint4*>(k_pool + (((size_t)page * G + c) * page_size + in_page + j) * hd + d0);
+        *reinterpret_cast<uint4*>(k_s + ((size_t)c * KT + j) * KS + d0) = v;
+      }
+    } else {
+      const int total = G * KT * hdp;
+      for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int c = idx / (KT * hdp), rest = idx - c * (KT * hdp);
+        const int j = rest / hdp, d = rest - j * hdp;
+        T v = from_f32<T>(0.f);
+        if (page >= 0 && key0 + j < kv_len && d < hd)
+          v = k_pool[(((size_t)page * G + c) * page_size + in_page + j) * hd + d];
+        k_s[((size_t)c * KT + j) * KS + d] = v;
+      }
+    }
+    // values: cached [dim][position], staged [c][j][dim]; a thread takes EV positions of one dimension, and the
+    // threads of a warp neighbouring dimensions (their stores fall in different banks)
+    {
+      const int chunks = KT / EV, total = G * chunks * vd;
+      for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int c = idx / (chunks * vd), rest = idx - c * (chunks * vd);
+        const int ch = rest / vd, d = rest - ch * vd;
+        float f[EV];
+#pragma unroll
+        for (int u = 0; u < EV; u++) f[u] = 0.f;
+        if (page >= 0)
+          AmxPiece<T>::load(v_pool + (((size_t)page * G + c) * vd + d) * page_size + in_page + ch * EV, f);
+#pragma unroll
+        for (int u = 0; u < EV; u++) {
+          const int j = ch * EV + u;
+          v_s[((size_t)c * KT + j) * vdp + d] = from_f32<T>(key0 + j < kv_len ? f[u] : 0.f);
+        }
+      }
+    }
+    __syncthreads();
+    // raw scores of this warp's pairs, a lane per key
+    {
+      float sc[RPW];
+#pragma unroll
+      for (int r = 0; r < RPW; r++) sc[r] = 0.f;
+      if (same_c) {
+        const T* kr = k_s + ((size_t)pr_c[0] * KT + jc) * KS;
+        for (int d0 = 0; d0 < hdp; d0 += EV) {
+          float kf[EV];
+          AmxPiece<T>::load(kr + d0, kf);
+#pragma unroll
+          for (int r = 0; r < RPW; r++) {
+            const float* qr = q_s + (size_t)(warp + nw * r < NP ? warp + nw * r : 0) * hdp + d0;
+#pragma unroll
+            for (int u = 0; u < EV; u += 4) {
+              const float4 qv = *reinterpret_cast<const float4*>(qr + u);
+              sc[r] = fmaf(qv.x, kf[u], sc[r]);
+              sc[r] = fmaf(qv.y, kf[u + 1], sc[r]);
+              sc[r] = fmaf(qv.z, kf[u + 2], sc[r]);
+              sc[r] = fmaf(qv.w, kf[u + 3], sc[r]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < RPW; r++) {
+          const T* kr = k_s + ((size_t)pr_c[r] * KT + jc) * KS;
+          const float* qr = q_s + (size_t)(warp + nw * r < NP ? warp + nw * r : 0) * hdp;
+          for (int d0 = 0; d0 < hdp; d0 += EV) {
+            float kf[EV];
+            AmxPiece<T>::load(kr + d0, kf);
+#pragma unroll
+            for (int u = 0; u < EV; u += 4) {
+              const float4 qv = *reinterpret_cast<const float4*>(qr + d0 + u);
+              sc[r] = fmaf(qv.x, kf[u], sc[r]);
+              sc[r] = fmaf(qv.y, kf[u + 1], sc[r]);
+              sc[r] = fmaf(qv.z, kf[u + 2], sc[r]);
+              sc[r] = fmaf(qv.w, kf[u + 3], sc[r]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RPW; r++)
+        if (warp + nw * r < NP && lane < KT) raw_s[(size_t)(warp + nw * r) * KT + lane] = sc[r] * scale;
+    }
+    __syncthreads();
+    // mixing across heads, mask, streaming softmax; the weights of the tile to p_s
+#pragma unroll
+    for (int r = 0; r < RPW; r++) {
+      if (warp + nw * r >= NP) continue;      // warp-uniform
+      const int p = warp + nw * r;
+      const int pos = pos_lo + pr_i[r], key = key0 + lane;
+      float t = 0.f;
+      if (lane < KT) {
+        const float* row = raw_s + (size_t)pr_i[r] * H * KT + lane;
+        const float* tk = talk_s + pr_h[r] * H;
+        for (int g = 0; g < H; g++) t = fmaf(tk[g], row[(size_t)g * KT], t);
+      }
+      const bool seen = lane < KT && pr_on[r] && key <= pos && (window <= 0 || pos - key < window);
+      const float tmax = warp_max(seen ? t : AMX_NEG);
+      const float m_new = fmaxf(mx[r], tmax);
+      const float w = seen ? expf(t - m_new) : 0.f;
+      const float corr = expf(mx[r] - m_new);      // 1 while nothing was seen (both at the floor)
+      l[r] = l[r] * corr + warp_sum(w);
+      mx[r] = m_new;
+#pragma unroll
+      for (int jj = 0; jj < HDL; jj++) acc[r][jj] *= corr;
+      if (lane < KT) p_s[(size_t)p * KT + lane] = w;
+    }
+    __syncwarp();
+    // weighted values, a lane per dimension; four keys' weights per read
+    if (same_c) {
+      const T* vb = v_s + (size_t)pr_c[0] * KT * vdp;
+      for (int j = 0; j < KT; j += 4) {
+        float4 pw[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; r++)
+          pw[r] = *reinterpret_cast<const float4*>(p_s + (size_t)(warp + nw * r < NP ? warp + nw * r : 0) * KT + j);
+#pragma unroll
+        for (int jj = 0; jj < HDL; jj++) {
+          const int d = lane + 32 * jj;
+          if (d >= vd) break;
+          const float v0 = to_f32(vb[(size_t)(j + 0) * vdp + d]), v1 = to_f32(vb[(size_t)(j + 1) * vdp + d]);
+          const float v2 = to_f32(vb[(size_t)(j + 2) * vdp + d]), v3 = to_f32(vb[(size_t)(j + 3) * vdp + d]);
+#pragma unroll
+          for (int r = 0; r < RPW; r++) {
+            acc[r][jj] = fmaf(pw[r].x, v0, acc[r][jj]);
+            acc[r][jj] = fmaf(pw[r].y, v1, acc[r][jj]);
+            acc[r][jj] = fmaf(pw[r].z, v2, acc[r][jj]);
+            acc[r][jj] = fmaf(pw[r].w, v3, acc[r][jj]);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < RPW; r++) {
+        if (warp + nw * r >= NP) continue;
+        const T* vb = v_s + (size_t)pr_c[r] * KT * vdp;
+        const float* pw = p_s + (size_t)(warp + nw * r) * KT;
+        for (int j = 0; j < KT; j += 4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(pw + j);
+#pragma unroll
+          for (int jj = 0; jj < HDL; jj++) {
+            const int d = lane + 32 * jj;
+            if (d >= vd) break;
+            acc[r][jj] = fmaf(w4.x, to_f32(vb[(size_t)(j + 0) * vdp + d]), acc[r][jj]);
+            acc[r][jj] = fmaf(w4.y, to_f32(vb[(size_t)(j + 1) * vdp + d]), acc[r][jj]);
+            acc[r][jj] = fmaf(w4.z, to_f32(vb[(size_t)(j + 2) * vdp + d]), acc[r][jj]);
+            acc[r][jj] = fmaf(w4.w, to_f32(vb[(size_t)(j + 3) * vdp + d]), acc[r][jj]);
+          }
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int r = 0; r < RPW; r++) {
+    if (!pr_on[r]) continue;
+    const size_t m = (size_t)q0 + row_lo + pr_i[r];
+    const int h = pr_h[r];
+    if (n_splits == 1) {
+      const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+#pragma unroll
+      for (int jj = 0; jj < HDL; jj++) {
+        const int d = lane + 32 * jj;
+        if (d >= vd) break;
+        float o = acc[r][jj] * inv;
+        if (gate) o *= 1.0f / (1.0f + expf(-gate[m * ldg + (size_t)h * vd + d]));
+        out[(m * H + h) * vd + d] = from_f32<T>(o);
+      }
+    } else {
+      float* pp = part + ((m * H + h) * n_splits + split) * (size_t)(vd + 2);
+      if (lane == 0) { pp[0] = mx[r]; pp[1] = l[r]; }
+#pragma unroll
+      for (int jj = 0; jj < HDL; jj++) {
+        const int d = lane + 32 * jj;
+        if (d < vd) pp[2 + d] = acc[r][jj];
+      }
+    }
+  }
+}
+
+// The pieces of a cut key range put together: a warp per (row, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part, const float* __restrict__ gate, int ldg,
+                             size_t pairs, int H, int vd, int n_splits) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const size_t pair = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const float* pp = part + pair * n_splits * (size_t)(vd + 2);
+  float m = AMX_NEG;
+  for (int s = 0; s < n_splits; s++) m = fmaxf(m, pp[(size_t)s * (vd + 2)]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; s++) l += pp[(size_t)s * (vd + 2) + 1] * expf(pp[(size_t)s * (vd + 2)] - m);
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  const size_t row = pair / H;
+  const int h = (int)(pair - row * H);
+  for (int d = lane; d < vd; d += 32) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; s++) a += pp[(size_t)s * (vd + 2) + 2 + d] * expf(pp[(size_t)s * (vd + 2)] - m);
+    float o = a * inv;
+    if (gate) o *= 1.0f / (1.0f + expf(-gate[row * ldg + (size_t)h * vd + d]));
+    out[pair * vd + d] = from_f32<T>(o);
+  }
+}
+
+// Bytes of shared memory a block needs for the given shape.
+static size_t amx_smem(int H, int G, int hd, int vd, int QT, int KT, size_t esz) {
+  const int EV = (int)(16 / esz);
+  const int hdp = (hd + 7) & ~7, vdp = (vd + 7) & ~7, NP = QT * H;
+  return sizeof(float) * (size_t)(((H * H + 3) & ~3) + NP * hdp + 2 * NP * KT) + esz * (size_t)G * KT * (hdp + EV + vdp);
+}
+
+// out [M, H*vd] and q [M, H*hd] (row stride ldq) in the cache's type; part: float scratch of
+// M*H*n_splits*(vd+2) when n_splits > 1; talk [H, H] float; gate float [M, H*vd] with row stride ldg, or null.
+LEB_API int leb_attention_mixed(void* out, float* part, const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                int dtype, const int* block_table, int bt_width, const int* seq_slot, const int* seq_pos0,
+                                const int* seq_qstart, const int* seq_qlen, const float* talk, const float* gate, int ldg,
+                                int M, int B, int H, int G, int hd, int vd, int page_size, int window, float scale,
+                                int max_qlen, int n_splits, cudaStream_t st) {
+  if (M <= 0 || B <= 0) return 0;
+  LEB_REQUIRE(H >= 1 && G >= 1 && H % G == 0, "leb_attention_mixed: %d heads do not divide into %d kv heads", H, G);
+  LEB_REQUIRE(H <= 128, "leb_attention_mixed: %d heads (a block mixes all heads of a row: up to 128)", H);
+  LEB_REQUIRE(hd >= 1 && hd <= 512 && vd >= 1 && vd <= 256, "leb_attention_mixed: head sizes %d / %d (up to 512 / 256)", hd, vd);
+  LEB_REQUIRE(page_size % 32 == 0, "leb_attention_mixed: pages of %d positions", page_size);
+  LEB_REQUIRE(n_splits >= 1 && (n_splits == 1 || part), "leb_attention_mixed: %d splits need scratch", n_splits);
+  LEB_REQUIRE(B <= 65535 && n_splits <= 65535, "leb_attention_mixed: step too large");
+  LEB_REQUIRE(dtype == LEB_F32 || dtype == LEB_BF16, "leb_attention_mixed: unknown dtype %d", dtype);
+  const size_t esz = dtype == LEB_BF16 ? 2 : 4;
+  // rows of a block: up to 128 (row, head) pairs, fewer when a sequence brings fewer rows; keys of a tile: 32, or
+  // fewer where the tiles of all kv heads would not fit
+  const size_t budget = 200 * 1024;
+  int QT = max(1, min(max_qlen, min(16, 128 / H)));
+  int KT = 32;
+  while (amx_smem(H, G, hd, vd, QT, KT, esz) > budget && QT > 1) QT = (QT + 1) / 2;
+  while (amx_smem(H, G, hd, vd, QT, KT, esz) > budget && KT > 8) KT /= 2;
+  const size_t smem = amx_smem(H, G, hd, vd, QT, KT, esz);
+  LEB_REQUIRE(smem <= 227 * 1024, "leb_attention_mixed: %d kv heads of %d / %d do not fit shared memory", G, hd, vd);
+  const int NP = QT * H;
+  int warps = min(AMX_MAX_WARPS, max(4, NP));
+  int rpw = ceil_div(NP, warps);
+  rpw = rpw <= 1 ? 1 : rpw <= 2 ? 2 : rpw <= 4 ? 4 : 8;
+  warps = max(4, min(AMX_MAX_WARPS, ceil_div(NP, rpw)));
+  const int hdl = ceil_div(vd, 32);
+  const dim3 grid(ceil_div(max_qlen, QT), n_splits, B), block(32 * warps);
+  LebPlainLaunches plain(true);
+#define AMX_LAUNCH(T_, HDL_, RPW_)                                                                                          \
+  {                                                                                                                         \
+    static size_t set = 48 * 1024;                                                                                          \
+    if (smem > set) {                                                                                                       \
+      if (cudaFuncSetAttribute(attention_mixed_kernel<T_, HDL_, RPW_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                               (int)smem) != cudaSuccess)                                                                   \
+        return leb_fail("leb_attention_mixed: %zu bytes of shared memory per block refused", smem);                        \
+      set = smem;                                                                                                           \
+    }                                                                                                                       \
+    leb_launch(attention_mixed_kernel<T_, HDL_, RPW_>, grid, block, smem, st, (T_*)out, part, (const T_*)q, ldq,            \
+               (const T_*)k_pool, (const T_*)v_pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen, talk, \
+               gate, ldg, H, G, hd, vd, page_size, window, scale, QT, KT, n_splits);                                        \
+  }
+#define AMX_RPW(T_, HDL_)                       \
+  {                                             \
+    if (rpw == 1) AMX_LAUNCH(T_, HDL_, 1)       \
+    else if (rpw == 2) AMX_LAUNCH(T_, HDL_, 2)  \
+    else if (rpw == 4) AMX_LAUNCH(T_, HDL_, 4)  \
+    else AMX_LAUNCH(T_, HDL_, 8)                \
+  }
+#define AMX_HDL(T_)                             \
+  {                                             \
+    if (hdl <= 1) AMX_RPW(T_, 1)                \
+    else if (hdl <= 2) AMX_RPW(T_, 2)           \
+    else if (hdl <= 4) AMX_RPW(T_, 4)           \
+    else AMX_RPW(T_, 8)                         \
+  }
+  if (dtype == LEB_F32) AMX_HDL(float)
+  else AMX_HDL(bf16)
+#undef AMX_HDL
+#undef AMX_RPW
+#undef AMX_LAUNCH
+  LEB_CHECK_LAUNCH("leb_attention_mixed");
+  if (n_splits > 1) {
+    const size_t pairs = (size_t)M * H;
+    const dim3 mgrid((unsigned)((pairs + 3) / 4)), mblock(128);
+    if (dtype == LEB_F32)
+      leb_launch(attention_mixed_merge_kernel<float>, mgrid, mblock, 0, st, (float*)out, part, gate, ldg, pairs, H, vd, n_splits);
+    else
+      leb_launch(attention_mixed_merge_kernel<bf16>, mgrid, mblock, 0, st, (bf16*)out, part, gate, ldg, pairs, H, vd, n_splits);
+    LEB_CHECK_LAUNCH("leb_attention_mixed (merge)");
+  }
+  return 0;
+}

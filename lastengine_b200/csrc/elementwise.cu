@@ -490,3 +490,115 @@ LEB_API int leb_scaled_residual(float* x, const float* y, float mult, void* h, i
   LEB_CHECK_LAUNCH("leb_scaled_residual");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Two layer norms of one row (weights w1 and w2, no bias): the mean and the variance are the row's, so
+// they are formed once and both results written.  For layers whose sublayers each read the stream
+// through a norm of their own.
+template <typename TO>
+__device__ __forceinline__ void layernorm_row2(TO* __restrict__ o1, TO* __restrict__ o2, const float* __restrict__ xi,
+                                               const float* __restrict__ w1, const float* __restrict__ w2, int D,
+                                               float eps, float* red) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) s += xi[i];
+  const float mean = block_sum(s, red) / (float)D;
+  float v = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float d = xi[i] - mean;
+    v += d * d;
+  }
+  const float r = 1.0f / sqrtf(block_sum(v, red) / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float t = (xi[i] - mean) * r;
+    o1[i] = from_f32<TO>(t * w1[i]);
+    o2[i] = from_f32<TO>(t * w2[i]);
+  }
+}
+
+// x[m, :] += mult * y[m, :] when y is given; then the two layer norms of the (new) row.
+template <typename TO>
+__global__ void layernorm_pair_kernel(TO* __restrict__ h1, TO* __restrict__ h2, float* __restrict__ x,
+                                      const float* __restrict__ y, float mult, const float* __restrict__ w1,
+                                      const float* __restrict__ w2, int D, float eps) {
+  __shared__ float red[33];
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  float* xr = x + m * D;
+  if (y) {
+    const float* yr = y + m * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) xr[i] = xr[i] + mult * yr[i];      // a thread re-reads only what it wrote
+  }
+  layernorm_row2(h1 + m * D, h2 + m * D, xr, w1, w2, D, eps, red);
+}
+
+LEB_API int leb_layernorm_pair(void* h1, void* h2, int dtype, float* x, const float* y, float mult, const float* w1,
+                               const float* w2, int M, int D, float eps, cudaStream_t st) {
+  if (M <= 0 || D <= 0) return 0;
+  LebPlainLaunches plain(true);
+  const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+  if (dtype == LEB_F32)
+    leb_launch(layernorm_pair_kernel<float>, dim3(M), dim3(threads), 0, st, (float*)h1, (float*)h2, x, y, mult, w1, w2, D, eps);
+  else if (dtype == LEB_BF16)
+    leb_launch(layernorm_pair_kernel<bf16>, dim3(M), dim3(threads), 0, st, (bf16*)h1, (bf16*)h2, x, y, mult, w1, w2, D, eps);
+  else
+    return leb_fail("leb_layernorm_pair: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_layernorm_pair");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// An activation without a gate, float in, the activation type out: 0 the erf form of gelu,
+// z/2 (1 + erf(z / sqrt 2)); 1 the square of relu; 2 the tanh form of gelu; 3 silu.  x may be a column
+// range of a wider result (row stride ldx).
+template <typename TO>
+__global__ void activation_kernel(TO* __restrict__ a, const float* __restrict__ x, int ldx, int F, size_t total, int act) {
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t m = i / F;
+  const int j = (int)(i - m * F);
+  const float z = x[m * ldx + j];
+  float r;
+  if (act == 0) r = 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+  else if (act == 1) { const float t = fmaxf(z, 0.f); r = t * t; }
+  else if (act == 2) r = gelu_tanh_f(z);
+  else r = z / (1.0f + expf(-z));
+  a[i] = from_f32<TO>(r);
+}
+
+LEB_API int leb_activation(void* a, int out_dtype, const float* x, int ldx, int M, int F, int act, cudaStream_t st) {
+  const size_t total = (size_t)M * F;
+  if (total == 0) return 0;
+  LEB_REQUIRE(act >= 0 && act <= 3, "leb_activation: unknown activation %d", act);
+  LebPlainLaunches plain(true);
+  const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  if (out_dtype == LEB_F32) leb_launch(activation_kernel<float>, grid, block, 0, st, (float*)a, x, ldx, F, total, act);
+  else if (out_dtype == LEB_BF16) leb_launch(activation_kernel<bf16>, grid, block, 0, st, (bf16*)a, x, ldx, F, total, act);
+  else return leb_fail("leb_activation: unknown dtype %d", out_dtype);
+  LEB_CHECK_LAUNCH("leb_activation");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Two sublayers' results side by side into one: out (+)= a (y1 + bias1) + b y2, all float [M, D];
+// bias1 [D] or null.
+__global__ void weighted_pair_sum_kernel(float* __restrict__ out, const float* __restrict__ y1, const float* __restrict__ bias1,
+                                         float a, const float* __restrict__ y2, float b, int D, size_t total, int accumulate) {
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float l = y1[i] + (bias1 ? bias1[i % D] : 0.f);
+  const float v = a * l + b * y2[i];
+  out[i] = accumulate ? out[i] + v : v;
+}
+
+LEB_API int leb_weighted_pair_sum(float* out, const float* y1, const float* bias1, float a, const float* y2, float b, int M,
+                                  int D, int accumulate, cudaStream_t st) {
+  const size_t total = (size_t)M * D;
+  if (total == 0) return 0;
+  LebPlainLaunches plain(true);
+  leb_launch(weighted_pair_sum_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, out, y1, bias1, a, y2, b, D,
+             total, accumulate);
+  LEB_CHECK_LAUNCH("leb_weighted_pair_sum");
+  return 0;
+}

@@ -1,0 +1,181 @@
+// Recurrences that run along a sequence one number at a time, and the small kernels around the matrix
+// memory with exponential gates.  Everything here is float: gates, their logarithms and exponentials, the
+// running maximum and the states are 32-bit whatever the model's activation type is.
+//
+// leb_min_gru: per channel S_t = (1 - z_t) S_(t-1) + z_t c_t with z = sigmoid(pz + bz) and the candidate
+//   c = u + 1/2 for u >= 0, sigmoid(u) below (u = px + bx); the row's result is S_t * silu(pg).  One state
+//   number per channel and sequence.  A thread owns a channel of a sequence and walks the step's rows in order;
+//   the rows' inputs are asked for a few rows ahead, so the walk waits on arithmetic, not on memory.
+// leb_exp_gates: log input gate i = cap tanh((pi + bi) / cap), log forget gate f = logsigmoid(cap tanh((pf + bf) / cap));
+//   running maximum m_t = max(f_t + m_(t-1), i_t) from the sequence's carried m (zero at its start);
+//   decay a_t = exp(f_t + m_(t-1) - m_t), write strength b_t = exp(i_t - m_t).  The gates of all rows are formed
+//   side by side, the maximum walks the rows, the exponentials are again side by side.
+// leb_exp_gates_finish: a head's read-out y [e] with its normaliser n.q in column e, both still without the
+//   query's scale s: o = s y / (max(|s n.q|, exp(-m_t)) + 1e-6); o over its root mean square (eps inside the
+//   root), times a weight over all heads' columns, times sigmoid(gate).
+#include "common.cuh"
+
+__device__ __forceinline__ float gs_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float gs_log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+constexpr int GRU_AHEAD = 4;      // rows whose inputs are in flight while one is computed
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+min_gru_kernel(TO* __restrict__ out, const float* __restrict__ pz, const float* __restrict__ px, const float* __restrict__ pg,
+               int ldp, const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state,
+               const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen, int W) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const int b = blockIdx.y;
+  const int slot = seq_slot[b];
+  const int n = seq_qlen ? seq_qlen[b] : 1;
+  const size_t m0 = seq_qstart[b];
+  const float zb = bz ? bz[c] : 0.f, xb = bx ? bx[c] : 0.f;
+  float S = slot >= 0 ? state[(size_t)slot * W + c] : 0.f;
+  float rz[GRU_AHEAD], rx[GRU_AHEAD], rg[GRU_AHEAD];
+#pragma unroll
+  for (int a = 0; a < GRU_AHEAD; a++)
+    if (a < n) {
+      rz[a] = pz[(m0 + a) * ldp + c];
+      rx[a] = px[(m0 + a) * ldp + c];
+      rg[a] = pg[(m0 + a) * ldp + c];
+    }
+  for (int t0 = 0; t0 < n; t0 += GRU_AHEAD) {
+#pragma unroll
+    for (int a = 0; a < GRU_AHEAD; a++) {
+      const int t = t0 + a;
+      if (t >= n) break;
+      const float zr = rz[a], u = rx[a] + xb, g = rg[a];
+      if (t + GRU_AHEAD < n) {
+        rz[a] = pz[(m0 + t + GRU_AHEAD) * ldp + c];
+        rx[a] = px[(m0 + t + GRU_AHEAD) * ldp + c];
+        rg[a] = pg[(m0 + t + GRU_AHEAD) * ldp + c];
+      }
+      const float z = gs_sigmoid(zr + zb);
+      const float cand = u >= 0.f ? u + 0.5f : gs_sigmoid(u);
+      S = (1.0f - z) * S + z * cand;
+      out[(m0 + t) * W + c] = from_f32<TO>(S * (g / (1.0f + expf(-g))));
+    }
+  }
+  if (slot >= 0) state[(size_t)slot * W + c] = S;
+}
+
+// out [M, W] in the activation type; pz, px, pg float with one row stride (column ranges of one projection);
+// bz, bx [W] or null; state [slots][W]; seq_qlen null: one row per sequence.
+LEB_API int leb_min_gru(void* out, int dtype, const float* pz, const float* px, const float* pg, int ldp, const float* bz,
+                        const float* bx, float* state, const int* seq_slot, const int* seq_qstart, const int* seq_qlen,
+                        int B, int W, cudaStream_t st) {
+  if (B <= 0 || W <= 0) return 0;
+  LEB_REQUIRE(B <= 65535, "leb_min_gru: step too large");
+  LebPlainLaunches plain(true);
+  const dim3 grid(ceil_div(W, 128), B), block(128);
+  if (dtype == LEB_F32)
+    leb_launch(min_gru_kernel<float>, grid, block, 0, st, (float*)out, pz, px, pg, ldp, bz, bx, state, seq_slot, seq_qstart,
+               seq_qlen, W);
+  else if (dtype == LEB_BF16)
+    leb_launch(min_gru_kernel<bf16>, grid, block, 0, st, (bf16*)out, pz, px, pg, ldp, bz, bx, state, seq_slot, seq_qstart,
+               seq_qlen, W);
+  else
+    return leb_fail("leb_min_gru: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_min_gru");
+  return 0;
+}
+
+// A block takes a sequence.  decay and write hold f and i between the phases; mrow gets m_t of every row.
+__global__ void __launch_bounds__(256)
+exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __restrict__ mrow, const float* __restrict__ pi,
+                 const float* __restrict__ pf, int ldp, const float* __restrict__ bi, const float* __restrict__ bf, float cap,
+                 float* __restrict__ mstate, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                 const int* __restrict__ seq_qlen, int H) {
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int slot = seq_slot[b];
+  const int n = seq_qlen ? seq_qlen[b] : 1;
+  const size_t m0 = seq_qstart[b];
+  for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
+    const int t = idx / H, h = idx - t * H;
+    const float ri = pi[(m0 + t) * ldp + h] + (bi ? bi[h] : 0.f);
+    const float rf = pf[(m0 + t) * ldp + h] + (bf ? bf[h] : 0.f);
+    write[(m0 + t) * H + h] = cap * tanhf(ri / cap);
+    decay[(m0 + t) * H + h] = gs_log_sigmoid(cap * tanhf(rf / cap));
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float m = slot >= 0 ? mstate[(size_t)slot * H + h] : 0.f;
+    for (int t = 0; t < n; t++) {
+      m = fmaxf(decay[(m0 + t) * H + h] + m, write[(m0 + t) * H + h]);
+      mrow[(m0 + t) * H + h] = m;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
+    const int t = idx / H, h = idx - t * H;
+    const float before = t > 0 ? mrow[(m0 + t - 1) * H + h] : (slot >= 0 ? mstate[(size_t)slot * H + h] : 0.f);
+    const float now = mrow[(m0 + t) * H + h];
+    const float f = decay[(m0 + t) * H + h], i = write[(m0 + t) * H + h];
+    decay[(m0 + t) * H + h] = expf(f + before - now);
+    write[(m0 + t) * H + h] = expf(i - now);
+  }
+  __syncthreads();      // every read of the carried maximum is done
+  if (slot >= 0 && n > 0)
+    for (int h = threadIdx.x; h < H; h += blockDim.x) mstate[(size_t)slot * H + h] = mrow[(m0 + n - 1) * H + h];
+}
+
+// decay, write, mrow [M, H] float; pi, pf float with one row stride; bi, bf [H] or null; mstate [slots][H].
+LEB_API int leb_exp_gates(float* decay, float* write, float* mrow, const float* pi, const float* pf, int ldp, const float* bi,
+                          const float* bf, float cap, float* mstate, const int* seq_slot, const int* seq_qstart,
+                          const int* seq_qlen, int B, int H, cudaStream_t st) {
+  if (B <= 0 || H <= 0) return 0;
+  LEB_REQUIRE(cap > 0.f, "leb_exp_gates: the gates' cap must be positive, got %g", (double)cap);
+  LebPlainLaunches plain(true);
+  leb_launch(exp_gates_kernel, dim3(B), dim3(256), 0, st, decay, write, mrow, pi, pf, ldp, bi, bf, cap, mstate, seq_slot,
+             seq_qstart, seq_qlen, H);
+  LEB_CHECK_LAUNCH("leb_exp_gates");
+  return 0;
+}
+
+// A warp takes a (row, head): y [M, H (e + 1)] with the normaliser's product in a head's last column.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+exp_gates_finish_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ mrow,
+                        const float* __restrict__ gate, int ldg, const float* __restrict__ w, float qscale, float eps, int M,
+                        int H, int e) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const size_t pair = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= (size_t)M * H) return;
+  const size_t m = pair / H;
+  const int h = (int)(pair - m * H);
+  const float* yr = y + (m * H + h) * (size_t)(e + 1);
+  const float den = fmaxf(fabsf(qscale * yr[e]), expf(-mrow[m * H + h])) + 1e-6f;
+  float ss = 0.f;
+  for (int i = lane; i < e; i += 32) {
+    const float o = qscale * yr[i] / den;
+    ss += o * o;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)e + eps);
+  for (int i = lane; i < e; i += 32) {
+    const float o = qscale * yr[i] / den;
+    const float g = gate[m * ldg + (size_t)h * e + i];
+    out[(m * H + h) * (size_t)e + i] = from_f32<TO>(o * r * w[(size_t)h * e + i] * gs_sigmoid(g));
+  }
+}
+
+LEB_API int leb_exp_gates_finish(void* out, int dtype, const float* y, const float* mrow, const float* gate, int ldg,
+                                 const float* w, float qscale, float eps, int M, int H, int e, cudaStream_t st) {
+  if (M <= 0 || H <= 0 || e <= 0) return 0;
+  LebPlainLaunches plain(true);
+  const size_t pairs = (size_t)M * H;
+  const dim3 grid((unsigned)((pairs + 3) / 4)), block(128);
+  if (dtype == LEB_F32)
+    leb_launch(exp_gates_finish_kernel<float>, grid, block, 0, st, (float*)out, y, mrow, gate, ldg, w, qscale, eps, M, H, e);
+  else if (dtype == LEB_BF16)
+    leb_launch(exp_gates_finish_kernel<bf16>, grid, block, 0, st, (bf16*)out, y, mrow, gate, ldg, w, qscale, eps, M, H, e);
+  else
+    return leb_fail("leb_exp_gates_finish: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_exp_gates_finish");
+  return 0;
+}

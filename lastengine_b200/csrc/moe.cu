@@ -22,9 +22,16 @@
 // only experts of the `keep` best groups (ties to the lower group) can be chosen: the others' c counts as minus
 // infinity.  Weights: the chosen s over their sum (+ 1e-20).
 #define ROUTER_SOFTMAX_GROUPED 3
+// The grouped sigmoid router (mode ROUTER_SIGMOID_GROUPED, groups and kept groups above the mode as for the grouped
+// softmax, and above those how many of a group's best choice scores add up to the group's score, 0 or 1: the best
+// alone): scores s = sigmoid(z), choice scores c = s + bias, groups and minus infinity as above; weights: the chosen s
+// over their sum (+ 1e-20), times the scaling factor.
+#define ROUTER_SIGMOID_GROUPED 4
 #define ROUTER_MODE(m) ((m) & 255)
 #define ROUTER_GROUPS(m) (((m) >> 8) & 255)
 #define ROUTER_KEEP(m) (((m) >> 16) & 255)
+#define ROUTER_GROUP_TOP(m) (((m) >> 24) & 15)
+#define ROUTER_GROUPED(m) (ROUTER_MODE(m) == ROUTER_SOFTMAX_GROUPED || ROUTER_MODE(m) == ROUTER_SIGMOID_GROUPED)
 __device__ __forceinline__ void router_score(float* s, float* c, float z, float b, int mode) {
   if (ROUTER_MODE(mode) == ROUTER_SOFTMAX_GROUPED) {
     *s = *c = z;       // the logit for now: router_softmax_groups turns a row's logits into s and c
@@ -37,9 +44,36 @@ __device__ __forceinline__ void router_score(float* s, float* c, float z, float 
   }
 }
 
-// One row of the grouped softmax router by one warp, between the logits and the choice.
+// The sum of the `top` largest of n numbers (top >= 1; every number counts once, equal ones in index order).
+__device__ __forceinline__ float router_top_sum(const float* c, int n, int top) {
+  if (top <= 1) {
+    float gs = -INFINITY;
+    for (int q = 0; q < n; q++) gs = fmaxf(gs, c[q]);
+    return gs;
+  }
+  float sum = 0.f, last = INFINITY;
+  int last_q = -1;
+  for (int j = 0; j < top && j < n; j++) {
+    float bv = -INFINITY;
+    int bq = -1;
+    for (int q = 0; q < n; q++) {
+      const bool after = c[q] < last || (c[q] == last && q > last_q);      // not taken yet
+      if (after && (bq < 0 || c[q] > bv)) { bv = c[q]; bq = q; }
+    }
+    if (bq < 0) break;
+    sum += bv;
+    last = bv;
+    last_q = bq;
+  }
+  return sum;
+}
+
+// One row of a grouped router by one warp, between the scores and the choice: a softmax over the logits first when
+// `softmax` is set (otherwise s and c are final already), then the experts outside the best groups lose their c.
 __device__ __forceinline__ void router_softmax_groups(float* __restrict__ s, float* __restrict__ c,
-                                                      const float* __restrict__ bias, int E, int groups, int keep, int lane) {
+                                                      const float* __restrict__ bias, int E, int groups, int keep, int lane,
+                                                      bool softmax = true, int group_top = 1) {
+  if (softmax) {
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
   mx = warp_max(mx);
@@ -50,6 +84,7 @@ __device__ __forceinline__ void router_softmax_groups(float* __restrict__ s, flo
     const float p = expf(s[e] - mx) / sum;
     s[e] = p;
     c[e] = p + (bias ? bias[e] : 0.f);
+  }
   }
   __syncwarp();
   if (groups > 1 && keep < groups) {
@@ -63,8 +98,7 @@ __device__ __forceinline__ void router_softmax_groups(float* __restrict__ s, flo
         const unsigned long long bit = 1ull << (g & 63);
         const unsigned long long word = g < 64 ? kept_lo : (g < 128 ? kept_hi : (g < 192 ? kept_2 : kept_3));
         if (word & bit) continue;
-        float gs = -INFINITY;
-        for (int q = 0; q < per; q++) gs = fmaxf(gs, c[g * per + q]);
+        const float gs = router_top_sum(c + g * per, per, group_top);
         if (bg < 0 || gs > bv) { bv = gs; bg = g; }
       }
       const unsigned long long bit = 1ull << (bg & 63);
@@ -108,7 +142,7 @@ __device__ __forceinline__ void router_choose(int* __restrict__ ids, float* __re
   if (lane == 0) {
     for (int j = 0; j < k; j++) {
       float w = norm_topk == ROUTER_SOFTMAX_CHOSEN ? expf(sg[chosen[j]] - sg[chosen[0]]) : sg[chosen[j]];
-      if (ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED) w = w / (sum + 1e-20f);
+      if (ROUTER_GROUPED(norm_topk)) w = w / (sum + 1e-20f);
       else if (norm_topk) w = w / sum;
       ids[j] = chosen[j];
       wts[j] = w * scaling;
@@ -185,8 +219,9 @@ moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, const 
   // the k largest c of each row, ties to the lower index: warp r' takes rows r', r' + warps, ...
   for (int r = warp; r < R; r += nw) {
     if (m0 + r >= M) continue;
-    if (ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED)
-      router_softmax_groups(s_ + r * E, c_ + r * E, bias, E, ROUTER_GROUPS(norm_topk), ROUTER_KEEP(norm_topk), lane);
+    if (ROUTER_GROUPED(norm_topk))
+      router_softmax_groups(s_ + r * E, c_ + r * E, bias, E, ROUTER_GROUPS(norm_topk), ROUTER_KEEP(norm_topk), lane,
+                            ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED, ROUTER_GROUP_TOP(norm_topk));
     router_choose(topk_ids + (size_t)(m0 + r) * k, topk_w + (size_t)(m0 + r) * k, c_ + r * E, s_ + r * E, E, k, norm_topk,
                   scaling, lane);
   }
@@ -279,8 +314,9 @@ moe_router_rows_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, c
   __syncthreads();
   for (int r = warp; r < RB; r += 8) {
     if (m0 + r >= M) continue;
-    if (ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED)
-      router_softmax_groups(s_ + r * E, c_ + r * E, bias, E, ROUTER_GROUPS(norm_topk), ROUTER_KEEP(norm_topk), lane);
+    if (ROUTER_GROUPED(norm_topk))
+      router_softmax_groups(s_ + r * E, c_ + r * E, bias, E, ROUTER_GROUPS(norm_topk), ROUTER_KEEP(norm_topk), lane,
+                            ROUTER_MODE(norm_topk) == ROUTER_SOFTMAX_GROUPED, ROUTER_GROUP_TOP(norm_topk));
     router_choose(topk_ids + (size_t)(m0 + r) * k, topk_w + (size_t)(m0 + r) * k, c_ + r * E, s_ + r * E, E, k, norm_topk,
                   scaling, lane);
   }

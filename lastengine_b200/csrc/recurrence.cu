@@ -56,7 +56,7 @@ gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restric
                         const float* __restrict__ v, int ldv, const float* __restrict__ wr, int ldw,
                         const float* __restrict__ decay, int ldd, const float* __restrict__ skip,
                         float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
-                        const int* __restrict__ seq_qlen, int H, int Gk, int d, int e, int wide) {
+                        const int* __restrict__ seq_qlen, int H, int Gk, int d, int e, int ev, int wide) {
   extern __shared__ __align__(16) float rec_sm[];
   constexpr int DP = 32 * NV;                   // a staged row of k, q or the decay
   constexpr int DA = ROW_DECAY ? DP : 1;
@@ -117,7 +117,8 @@ gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restric
     for (int idx = threadIdx.x; idx < rows * (REC_COLS + 2); idx += blockDim.x) {
       const int t = idx / (REC_COLS + 2), jj = idx - t * (REC_COLS + 2);
       if (jj < REC_COLS) {
-        if (c0 + jj < e) rec_copy4(vs + t * REC_COLS + jj, v + (m + t) * ldv + h * e + c0 + jj);
+        if (c0 + jj < ev) rec_copy4(vs + t * REC_COLS + jj, v + (m + t) * ldv + h * ev + c0 + jj);
+        else if (c0 + jj < e) vs[t * REC_COLS + jj] = 1.0f;      // columns past the values' width hold a constant one
       } else if (jj == REC_COLS) {
         rec_copy4(ws + t, wr + (m + t) * ldw + h);
       } else if (!ROW_DECAY) {
@@ -212,13 +213,17 @@ gated_recurrence_kernel(float* __restrict__ out, int ldo, const float* __restric
   }
 }
 
-// out [M, H*e]; k, q [M, Gk*d] with the row stride ldk; v [M, H*e]; write [M, H]; decay [M, H*d] when
+// out [M, H*e]; k, q [M, Gk*d] with the row stride ldk; v [M, H*ev]; write [M, H]; decay [M, H*d] when
 // row_decay, else [M, H]; skip [H] or null; state [slots][H][e][d].  seq_qlen null: one row per sequence.
+// ev < e: a head's value has ev numbers and the state's columns ev .. e-1 are written with the value one, so
+// that column accumulates the keys alone (decayed and weighted like the rest) and its read-out is the
+// product of that sum with the query: the normaliser of a memory whose result is divided by it.
 LEB_API int leb_gated_recurrence(float* out, int ldo, const float* k, const float* q, int ldk, const float* v, int ldv,
                                  const float* write, int ldw, const float* decay, int ldd, int row_decay, int delta,
                                  const float* skip, float* state, const int* seq_slot, const int* seq_qstart,
-                                 const int* seq_qlen, int B, int H, int Gk, int d, int e, cudaStream_t st) {
+                                 const int* seq_qlen, int B, int H, int Gk, int d, int e, int ev, cudaStream_t st) {
   if (B <= 0) return 0;
+  LEB_REQUIRE(ev >= 0 && ev <= e, "leb_gated_recurrence: %d value columns for a state of %d", ev, e);
   LEB_REQUIRE(H >= 1 && Gk >= 1 && H % Gk == 0, "leb_gated_recurrence: %d heads do not divide into %d key heads", H, Gk);
   LEB_REQUIRE(d >= 1 && d <= 256 && e >= 1, "leb_gated_recurrence: a state of %d x %d (rows 1..256)", d, e);
   LEB_REQUIRE(H <= 65535 && B <= 65535, "leb_gated_recurrence: step too large");
@@ -238,7 +243,7 @@ LEB_API int leb_gated_recurrence(float* out, int ldo, const float* k, const floa
       set = smem;                                                                                                        \
     }                                                                                                                    \
     leb_launch(gated_recurrence_kernel<NV_, D_, R_>, grid, block, smem, st, out, ldo, k, q, ldk, v, ldv, write, ldw, decay, \
-               ldd, skip, state, seq_slot, seq_qstart, seq_qlen, H, Gk, d, e, wide);                                     \
+               ldd, skip, state, seq_slot, seq_qstart, seq_qlen, H, Gk, d, e, ev, wide);                                     \
   }
 #define LEB_REC2(NV_)                                     \
   {                                                       \

@@ -152,7 +152,14 @@ def _declare(L) -> None:
         "leb_selftest_bounded_wait": [P, I, I, P],
         "leb_gemm_bf16_tc_slices": [I, I, I],
         "leb_gemm_bf16_tc_sliced": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
-        "leb_gated_recurrence": [P, I, P, P, I, P, I, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, P],
+        "leb_gated_recurrence": [P, I, P, P, I, P, I, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
+        "leb_min_gru": [P, I, P, P, P, I, P, P, P, P, P, P, I, I, P],
+        "leb_exp_gates": [P, P, P, P, P, I, P, P, F, P, P, P, P, I, I, P],
+        "leb_exp_gates_finish": [P, I, P, P, P, I, P, F, F, I, I, I, P],
+        "leb_layernorm_pair": [P, P, I, P, P, F, P, P, I, I, F, P],
+        "leb_activation": [P, I, P, I, I, I, I, P],
+        "leb_weighted_pair_sum": [P, P, P, F, P, F, I, I, I, P],
+        "leb_attention_mixed": [P, P, P, I, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
         "leb_delta_prep": [P, P, P, P, P, P, I, P, I, P, I, P, P, I, I, I, I, I, F, F, P],
         "leb_ssm_prep": [P, I, I, P, P, P, P, I, P, P, I, I, P],
         "leb_group_norm_gate": [P, I, P, P, I, P, I, I, I, I, F, I, P],
@@ -400,16 +407,20 @@ RECURRENCE_MAX_ROWS = 256     # rows of a head's state the recurrence kernel tak
 
 def gated_recurrence(out: torch.Tensor, k: torch.Tensor, q: torch.Tensor, v: torch.Tensor, write: torch.Tensor,
                      decay: torch.Tensor, state: torch.Tensor, batch, H: int, Gk: int, d: int, e: int,
-                     delta: bool, skip: torch.Tensor | None = None) -> None:
+                     delta: bool, skip: torch.Tensor | None = None, ones_columns: int = 0) -> None:
     """The linear recurrence of the step's rows with a state per sequence and head (all float):
         S <- diag(decay) S;  u = write * v (delta: write * (v - S^T k));  S <- S + k u^T;  o = S^T q (+ skip_h v)
     k, q [M, Gk*d] (one row stride), v [M, H*e], write [M, H], decay [M, H*d] (per key channel) or [M, H];
-    head h reads key head h // (H // Gk); state [slots, H, e, d] (a column of S is contiguous); out [M, H*e]."""
+    head h reads key head h // (H // Gk); state [slots, H, e, d] (a column of S is contiguous); out [M, H*e].
+    `ones_columns` n > 0: v has e - n columns per head and the state's last n columns are written with ones, so
+    they hold the (decayed, weighted) sum of the keys and their read-out is that sum's product with q."""
     M = out.shape[0]
+    ev = e - int(ones_columns)
+    assert 0 <= ev <= e and not (delta and ones_columns)
     ldo = _f32_rows(out, "gated_recurrence.out", M, H * e)
     ldk = _f32_rows(k, "gated_recurrence.k", M, Gk * d)
     assert _f32_rows(q, "gated_recurrence.q", M, Gk * d) == ldk
-    ldv = _f32_rows(v, "gated_recurrence.v", M, H * e)
+    ldv = _f32_rows(v, "gated_recurrence.v", M, H * ev)
     ldw = _f32_rows(write, "gated_recurrence.write", M, H)
     row_decay = decay.shape[1] == H * d and not (d == 1 and decay.shape[1] == H and False)
     if decay.shape[1] != H * d:
@@ -424,7 +435,7 @@ def gated_recurrence(out: torch.Tensor, k: torch.Tensor, q: torch.Tensor, v: tor
     _check(lib().leb_gated_recurrence(_ptr(out), ldo, _ptr(k), _ptr(q), ldk, _ptr(v), ldv, _ptr(write), ldw, _ptr(decay), ldd,
                                       1 if row_decay else 0, 1 if delta else 0, _ptr(skip), _ptr(state), _ptr(batch.seq_slot),
                                       _ptr(batch.seq_qstart), None if single else _ptr(batch.seq_qlen), batch.n_seqs,
-                                      H, Gk, d, e, _stream()))
+                                      H, Gk, d, e, ev, _stream()))
 
 
 def group_norm_gate(out: torch.Tensor, y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, group_size: int, eps: float,
@@ -440,6 +451,159 @@ def group_norm_gate(out: torch.Tensor, y: torch.Tensor, z: torch.Tensor, w: torc
     _cuda(w, "group_norm_gate.w", torch.float32)
     _check(lib().leb_group_norm_gate(_ptr(out), _dt(out, "group_norm_gate.out"), _ptr(y), _ptr(z), ldz, _ptr(w), M, C,
                                      int(group_size), w.numel(), float(eps), 1 if gate_first else 0, _stream()))
+
+
+def min_gru(out: torch.Tensor, pz: torch.Tensor, px: torch.Tensor, pg: torch.Tensor, bz: torch.Tensor | None,
+            bx: torch.Tensor | None, state: torch.Tensor, batch) -> None:
+    """The minimal gated recurrent unit over the step's rows, per channel and sequence (all float):
+    z = sigmoid(pz + bz), u = px + bx, c = u + 1/2 where u >= 0 else sigmoid(u), S <- (1 - z) S + z c,
+    out = S * silu(pg) in out's type.  pz, px, pg float [M, W] with one row stride; state [slots, W]."""
+    _cuda(out, "min_gru.out")
+    M, W = out.shape
+    ldp = _f32_rows(pz, "min_gru.pz", M, W)
+    assert _f32_rows(px, "min_gru.px", M, W) == ldp and _f32_rows(pg, "min_gru.pg", M, W) == ldp
+    for name, t in (("bz", bz), ("bx", bx)):
+        if t is not None:
+            _cuda(t, f"min_gru.{name}", torch.float32)
+            assert t.numel() == W
+    _cuda(state, "min_gru.state", torch.float32)
+    assert state.shape[1:] == (W,)
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_min_gru(_ptr(out), _dt(out, "min_gru.out"), _ptr(pz), _ptr(px), _ptr(pg), ldp, _ptr(bz), _ptr(bx),
+                             _ptr(state), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
+                             None if single else _ptr(batch.seq_qlen), batch.n_seqs, W, _stream()))
+
+
+def exp_gates(decay: torch.Tensor, write: torch.Tensor, mrow: torch.Tensor, pi: torch.Tensor, pf: torch.Tensor,
+              bi: torch.Tensor | None, bf: torch.Tensor | None, cap: float, mstate: torch.Tensor, batch) -> None:
+    """Exponential gates under a running maximum, per head and sequence (all float): i = cap tanh((pi + bi) / cap),
+    f = logsigmoid(cap tanh((pf + bf) / cap)), m_t = max(f_t + m_(t-1), i_t) from the carried m (mstate [slots, H]),
+    decay_t = exp(f_t + m_(t-1) - m_t), write_t = exp(i_t - m_t), mrow_t = m_t.  All [M, H]."""
+    _cuda(decay, "exp_gates.decay", torch.float32)
+    M, H = decay.shape
+    _cuda(write, "exp_gates.write", torch.float32)
+    _cuda(mrow, "exp_gates.mrow", torch.float32)
+    assert write.shape == (M, H) and mrow.shape == (M, H)
+    ldp = _f32_rows(pi, "exp_gates.pi", M, H)
+    assert _f32_rows(pf, "exp_gates.pf", M, H) == ldp
+    for name, t in (("bi", bi), ("bf", bf)):
+        if t is not None:
+            _cuda(t, f"exp_gates.{name}", torch.float32)
+            assert t.numel() == H
+    _cuda(mstate, "exp_gates.mstate", torch.float32)
+    assert mstate.shape[1:] == (H,)
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_exp_gates(_ptr(decay), _ptr(write), _ptr(mrow), _ptr(pi), _ptr(pf), ldp, _ptr(bi), _ptr(bf), float(cap),
+                               _ptr(mstate), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
+                               None if single else _ptr(batch.seq_qlen), batch.n_seqs, H, _stream()))
+
+
+def exp_gates_finish(out: torch.Tensor, y: torch.Tensor, mrow: torch.Tensor, gate: torch.Tensor, w: torch.Tensor,
+                     qscale: float, eps: float, H: int, e: int) -> None:
+    """The read-out of a memory with exponential gates on its way to the output projection: y float [M, H (e + 1)]
+    holds per head the read-out and, in its last column, the normaliser's product with the query, both still
+    without the query's scale; o = qscale y / (max(|qscale n.q|, exp(-m)) + 1e-6), divided by its root mean
+    square per head, times w [H e], times sigmoid(gate) (float [M, H e], a column range is fine)."""
+    _cuda(out, "exp_gates_finish.out")
+    M = out.shape[0]
+    assert out.shape == (M, H * e)
+    _cuda(y, "exp_gates_finish.y", torch.float32)
+    assert y.shape == (M, H * (e + 1))
+    _cuda(mrow, "exp_gates_finish.mrow", torch.float32)
+    assert mrow.shape == (M, H)
+    ldg = _f32_rows(gate, "exp_gates_finish.gate", M, H * e)
+    _cuda(w, "exp_gates_finish.w", torch.float32)
+    assert w.numel() == H * e
+    _check(lib().leb_exp_gates_finish(_ptr(out), _dt(out, "exp_gates_finish.out"), _ptr(y), _ptr(mrow), _ptr(gate), ldg,
+                                      _ptr(w), float(qscale), float(eps), M, H, e, _stream()))
+
+
+def layernorm_pair(h1: torch.Tensor, h2: torch.Tensor, x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, eps: float,
+                   y: torch.Tensor | None = None, mult: float = 1.0) -> None:
+    """Two layer norms (weights w1, w2, no bias) of the rows of x (float [M, D]) into h1 and h2; with `y` the
+    launch first adds mult * y into x."""
+    _cuda(x, "layernorm_pair.x", torch.float32)
+    M, D = x.shape
+    _cuda(h1, "layernorm_pair.h1")
+    _cuda(h2, "layernorm_pair.h2", h1.dtype)
+    assert h1.shape == (M, D) and h2.shape == (M, D)
+    _cuda(w1, "layernorm_pair.w1", torch.float32)
+    _cuda(w2, "layernorm_pair.w2", torch.float32)
+    assert w1.numel() == D and w2.numel() == D
+    if y is not None:
+        _cuda(y, "layernorm_pair.y", torch.float32)
+        assert y.shape == (M, D)
+    _check(lib().leb_layernorm_pair(_ptr(h1), _ptr(h2), _dt(h1, "layernorm_pair.h1"), _ptr(x), _ptr(y), float(mult),
+                                    _ptr(w1), _ptr(w2), M, D, float(eps), _stream()))
+
+
+GELU_ERF, RELU_SQUARED = 0, 1      # activations without a gate (leb_activation); 2 and 3: the tanh form of gelu, silu
+PLAIN_ACTIVATIONS = {"gelu": 0, "relu_squared": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def activation(out: torch.Tensor, x: torch.Tensor, act: int) -> None:
+    """out = act(x) in out's type; x float [M, F] (a column range is fine)."""
+    _cuda(out, "activation.out")
+    M, F_ = out.shape
+    ldx = _f32_rows(x, "activation.x", M, F_)
+    _check(lib().leb_activation(_ptr(out), _dt(out, "activation.out"), _ptr(x), ldx, M, F_, int(act), _stream()))
+
+
+def weighted_pair_sum(out: torch.Tensor, y1: torch.Tensor, a: float, y2: torch.Tensor, b: float,
+                      bias1: torch.Tensor | None = None, accumulate: bool = False) -> None:
+    """out (+)= a (y1 + bias1) + b y2, all float [M, D]."""
+    for n, t in (("out", out), ("y1", y1), ("y2", y2)):
+        _cuda(t, f"weighted_pair_sum.{n}", torch.float32)
+    M, D = out.shape
+    assert y1.shape == (M, D) and y2.shape == (M, D)
+    if bias1 is not None:
+        _cuda(bias1, "weighted_pair_sum.bias1", torch.float32)
+        assert bias1.numel() == D
+    _check(lib().leb_weighted_pair_sum(_ptr(out), _ptr(y1), _ptr(bias1), float(a), _ptr(y2), float(b), M, D,
+                                       1 if accumulate else 0, _stream()))
+
+
+def add_row_vector(out: torch.Tensor, vec: torch.Tensor) -> None:
+    """out[m, :] += vec (float)."""
+    weighted_pair_sum(out, out, 1.0, out, 0.0, bias1=vec)
+
+
+def mixed_attention_splits(batch, H: int, window: int) -> int:
+    """In how many pieces a decode step's key range is cut: one block takes all heads of a row, so a step of few
+    sequences would leave most SMs idle; pieces of at least 128 keys until the SMs have a block each."""
+    if batch.max_qlen > 1:
+        return 1
+    keys = batch.max_kvlen if window <= 0 else min(batch.max_kvlen, window)
+    return max(1, min(keys // 128, -(-sm_count() // max(1, batch.n_seqs)), 32))
+
+
+def attention_mixed(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                    batch, talk: torch.Tensor, gate: torch.Tensor | None, nh: int, nkv: int, hd: int, vd: int,
+                    page_size: int, window: int, scale: float, n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """Attention of the step's rows over the paged cache with the heads' scores mixed before the softmax:
+    t_h = sum_g talk[h, g] (scale q_g . k), softmax over the visible keys (causal, inside `window` when > 0),
+    weighted values, times sigmoid(gate) where a gate (float [M, nh vd], a column range is fine) is given."""
+    _cuda(out, "attention_mixed.out")
+    M = out.shape[0]
+    _cuda(q, "attention_mixed.q", out.dtype, contiguous=False)
+    assert out.shape == (M, nh * vd) and q.shape == (M, nh * hd) and q.stride(1) == 1
+    _cuda(k_pool, "attention_mixed.k_pool", out.dtype)
+    _cuda(v_pool, "attention_mixed.v_pool", out.dtype)
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, vd, page_size)
+    _cuda(block_table, "attention_mixed.block_table", torch.int32)
+    _cuda(talk, "attention_mixed.talk", torch.float32)
+    assert talk.shape == (nh, nh)
+    ldg = _f32_rows(gate, "attention_mixed.gate", M, nh * vd) if gate is not None else 0
+    if n_splits > 1:
+        need = M * nh * n_splits * (vd + 2)
+        if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"attention_mixed: {n_splits} splits need {need} floats of scratch")
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_attention_mixed(
+        _ptr(out), _ptr(scratch), _ptr(q), q.stride(0), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention_mixed"),
+        _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart),
+        None if single else _ptr(batch.seq_qlen), _ptr(talk), _ptr(gate), ldg, M, batch.n_seqs, nh, nkv, hd, vd, page_size,
+        int(window), float(scale), batch.max_qlen, int(n_splits), _stream()))
 
 
 def pooled_attn_prep(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, proj: torch.Tensor,
@@ -1284,13 +1448,15 @@ _OPTIONAL_TC: list = [None]
 # ----------------------------------------------------------------------------------------------
 def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr: torch.Tensor,
                bias: torch.Tensor | None, norm_topk: bool, scaling: float, softmax_chosen: bool = False,
-               softmax_groups: tuple[int, int] | None = None) -> None:
+               softmax_groups: tuple[int, int] | None = None, sigmoid_groups: tuple[int, int, int] | None = None) -> None:
     """The k experts of every row and their weights.  Default: sigmoid scores, the bias only chooses,
     weights are the chosen sigmoids (over their sum with norm_topk).  `softmax_chosen`: logits Wr h + bias,
     the k largest chosen, weights the softmax over the chosen logits alone.  `softmax_groups` = (groups, keep):
     scores are the softmax over all experts, the bias only chooses, only experts of the `keep` best of
     `groups` equal groups of neighbours (a group's score: its largest choice score) can be chosen, weights
-    are the chosen scores over their sum (+ 1e-20)."""
+    are the chosen scores over their sum (+ 1e-20).  `sigmoid_groups` = (groups, keep, top): sigmoid scores, the
+    bias only chooses, groups as before with a group's score the sum of its `top` largest choice scores, weights
+    the chosen scores over their sum (+ 1e-20) times `scaling`."""
     _cuda(topk_ids, "moe_router.topk_ids", torch.int32)
     _cuda(topk_w, "moe_router.topk_w", torch.float32)
     _cuda(h, "moe_router.h")
@@ -1307,6 +1473,12 @@ def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr
         if not (1 <= keep <= groups <= 255 and E % groups == 0 and keep * (E // groups) >= k):
             raise KernelError(f"moe_router: {keep} of {groups} groups over {E} experts cannot give {k} choices")
         mode = 3 | (groups << 8) | (keep << 16)
+    if sigmoid_groups is not None:
+        groups, keep, top = (int(v) for v in sigmoid_groups)
+        if not (1 <= keep <= groups <= 255 and E % groups == 0 and keep * (E // groups) >= k and 1 <= top <= 15):
+            raise KernelError(f"moe_router: {keep} of {groups} groups (ranked by their {top} best) over {E} experts "
+                              f"cannot give {k} choices")
+        mode = 4 | (groups << 8) | (keep << 16) | (top << 24)
     _check(lib().leb_moe_router(_ptr(topk_ids), _ptr(topk_w), _ptr(h), _dt(h, "moe_router.h"), _ptr(wr),
                                 _ptr(bias), M, D, E, k, mode, float(scaling), _stream()))
 

@@ -1,6 +1,7 @@
 """Arrangement of a layer's parts.
 
-parallel_residual (at the end of this file): x += mult * (Mixer(norm(x)) + FeedForward(norm(x))).
+parallel_residual (further down): x += mult * (Mixer(norm(x)) + FeedForward(norm(x))), with one norm for both
+sublayers or one each.
 
 pre_norm_residual (src/dense.rs:178-194):
     x += [post_norm](Mixer(norm(x)));  x += [post_norm](FeedForward(norm(x)))
@@ -196,23 +197,32 @@ class GatedPreNormResidualBlock:
 
 @BLOCKS.register("parallel_residual")
 class ParallelResidualBlock:
-    """h = norm(x);  x += mult * (Mixer(h) + FeedForward(h)): one norm, both sublayers read its result,
-    their results are summed in float and enter the stream together, times a constant.  A layer may have
-    no feed-forward.  The kernel that adds the sum into x also leaves the norm of the new x for the next
-    block when that is of this arrangement too (with a layer norm) and nothing is added to the stream in
-    between, so a model runs one norm kernel, for its first layer."""
+    """h = norm(x);  x += mult * (Mixer(h) + FeedForward(h)): both sublayers read the stream as it was before
+    the layer, their results are summed in float and enter the stream together, times a constant.  With one
+    norm both read its result; with `ffn_norm` the feed-forward reads a norm of its own (two layer norms of
+    the same row share its mean and variance and are formed by one launch).  A layer may have no feed-forward.
+    The kernel that adds the sum into x also leaves the norm (or the two norms) of the new x for the next block
+    when that is of this arrangement too (with layer norms) and nothing is added to the stream in between, so a
+    model runs one norm kernel, for its first layer."""
 
     def __init__(self, mixer, ffn, mixer_norm, ffn_norm=None, post_mixer_norm=None, post_ffn_norm=None,
                  mult: float = 1.0):
-        if ffn_norm is not None or post_mixer_norm is not None or post_ffn_norm is not None:
-            raise ValueError("the parallel arrangement has one norm, in front of both sublayers")
-        self.mixer, self.ffn, self.mixer_norm = mixer, ffn, mixer_norm
+        if post_mixer_norm is not None or post_ffn_norm is not None:
+            raise ValueError("the parallel arrangement has its norms in front of the sublayers")
+        if ffn_norm is not None and ffn is None:
+            raise ValueError("a feed-forward's norm without a feed-forward")
+        if ffn_norm is not None and (getattr(ffn_norm, "has_bias", True) or getattr(mixer_norm, "has_bias", True)
+                                     or ffn_norm.eps != mixer_norm.eps):
+            raise ValueError("two norms in front of parallel sublayers: layer norms without bias and with one eps")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
         self.mult = float(mult)
 
     def parts(self) -> dict[str, object]:
         p = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
         if self.ffn is not None:
             p["ffn"] = self.ffn
+        if self.ffn_norm is not None:
+            p["ffn_norm"] = self.ffn_norm
         return p
 
     def first_reader(self):
@@ -223,24 +233,41 @@ class ParallelResidualBlock:
         M, D = x.shape
         ws = env.workspace
         env.split_in = env.split_out = None
-        if isinstance(pending, NormedRows) and pending.norm is self.mixer_norm and pending.values.shape == (M, D):
+        two = self.ffn_norm is not None
+        first_set = ("block.h", "block.hb")
+        if (isinstance(pending, NormedRows) and pending.norm is self.mixer_norm and pending.values.shape == (M, D)
+                and (not two or getattr(pending, "second_norm", None) is self.ffn_norm)):
             h = pending.values
+            hf = pending.second if two else h
         else:
-            h = ws.get("block.h", (M, D), env.dtype)
-            self.mixer_norm.forward(h, x)
+            h = ws.get(first_set[0], (M, D), env.dtype)
+            if two:
+                hf = ws.get(first_set[1], (M, D), env.dtype)
+                kernels.layernorm_pair(h, hf, x, self.mixer_norm.weight, self.ffn_norm.weight, self.mixer_norm.eps)
+            else:
+                hf = h
+                self.mixer_norm.forward(h, x)
         y = ws.get("block.t", (M, D), torch.float32)
         self.mixer.forward(h, y, False, batch, cache, env)
         if self.ffn is not None:
-            self.ffn.forward(h, y, True, batch, env)
+            self.ffn.forward(hf, y, True, batch, env)
         nxt = env.next_block_norm
-        after = nxt[0] if nxt is not None and isinstance(nxt[1], ParallelResidualBlock) and isinstance(nxt[0], LayerNorm) \
-            else None
+        after = nxt[1] if nxt is not None and isinstance(nxt[1], ParallelResidualBlock) and isinstance(nxt[0], LayerNorm) \
+            and not nxt[0].has_bias else None
         if after is None:
             kernels.scaled_residual(x, y, self.mult)
             return None
-        h2 = ws.get("block.h2" if h is ws.get("block.h", (M, D), env.dtype) else "block.h", (M, D), env.dtype)
-        kernels.scaled_residual(x, y, self.mult, h=h2, norm_w=after.weight, eps=after.eps)
-        return NormedRows(h2, after)
+        names = ("block.h2", "block.hb2") if h is ws.get(first_set[0], (M, D), env.dtype) else first_set
+        h2 = ws.get(names[0], (M, D), env.dtype)
+        if after.ffn_norm is not None:
+            hf2 = ws.get(names[1], (M, D), env.dtype)
+            kernels.layernorm_pair(h2, hf2, x, after.mixer_norm.weight, after.ffn_norm.weight, after.mixer_norm.eps,
+                                   y=y, mult=self.mult)
+            left = NormedRows(h2, after.mixer_norm)
+            left.second, left.second_norm = hf2, after.ffn_norm
+            return left
+        kernels.scaled_residual(x, y, self.mult, h=h2, norm_w=after.mixer_norm.weight, eps=after.mixer_norm.eps)
+        return NormedRows(h2, after.mixer_norm)
 
 
 class StreamRows:

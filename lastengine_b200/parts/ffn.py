@@ -90,6 +90,38 @@ class SwiGLU(FeedForward):
                        emit=emit if accumulate else None)
 
 
+@FEED_FORWARDS.register("dense")
+class DenseFeedForward(FeedForward):
+    """f = W_down act(W_up h) without a gate; act is the erf form of gelu unless `activation` names another
+    ("relu_squared": max(z, 0)^2; "gelu_tanh"; "silu").  The up projection's float results go through the
+    activation in float.  `names`: (up, down)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu",
+                 names: tuple[str, str] = ("up", "down")):
+        if activation not in kernels.PLAIN_ACTIVATIONS:
+            raise ValueError(f"unknown feed-forward activation '{activation}' ({', '.join(sorted(kernels.PLAIN_ACTIVATIONS))})")
+        self.D, self.F = int(hidden_size), int(intermediate_size)
+        self.act = kernels.PLAIN_ACTIVATIONS[activation]
+        self.n_up, self.n_down = (str(n) for n in names)
+        self.w1 = self.w2 = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {self.n_up: TensorSpec((self.F, self.D), MATRIX), self.n_down: TensorSpec((self.D, self.F), MATRIX)}
+
+    def load(self, tensors, env: BuildEnv) -> None:
+        self.w1 = tensors[self.n_up].contiguous()
+        self.w2 = tensors[self.n_down].contiguous()
+
+    def forward(self, h, out, accumulate, batch, env) -> None:
+        M = h.shape[0]
+        ws = env.workspace
+        u = ws.get("ffn.u", (M, self.F), torch.float32)
+        kernels.linear(u, h, self.w1)
+        a = ws.get("ffn.a", (M, self.F), env.dtype)
+        kernels.activation(a, u, self.act)
+        kernels.linear(out, a, self.w2, kernels.ACCUMULATE if accumulate else kernels.STORE)
+
+
 @FEED_FORWARDS.register("sigmoid_topk_moe", "topk_moe")
 class SigmoidTopKMoE(FeedForward):
     """Top-k experts of the gated shape.  Defaults: the sigmoid router described at the top of this file and
@@ -103,6 +135,11 @@ class SigmoidTopKMoE(FeedForward):
     scores s + bias (the bias chooses, it does not weigh); the experts form `count` equal groups of neighbours,
     a group's score is its largest choice score, and only experts of the `keep` best groups can be chosen (the
     others' choice scores count as minus infinity); weights are the chosen s over their sum (+ 1e-20).
+    `router="sigmoid_grouped"` with `groups=(count, keep)` and `group_top`: sigmoid scores, the bias only chooses,
+    groups as above but a group's score is the sum of its `group_top` largest choice scores; weights are the
+    chosen s over their sum (+ 1e-20), times `scaling`.
+    `gated=False`: experts of the plain shape W_down act(W_up h) (no gate tensors) with `activation` one of
+    "gelu" (erf form), "relu_squared", "gelu_tanh", "silu".
     `shared_size` > 0: one more expert of that width and the same activation runs for every row and is added
     (tensors "shared_gate"/"shared_up"/"shared_down").
     `names`: "router", "bias", and "gate"/"up"/"down" with `{e}` standing for the expert's number."""
@@ -111,29 +148,37 @@ class SigmoidTopKMoE(FeedForward):
                  norm_topk: bool = True, use_bias: bool = True, scaling: float = 1.0,
                  bias_std: float = 0.1, router: str = "sigmoid", activation: str = "silu",
                  limit: float = 0.0, alpha: float = 1.0, names: dict[str, str] | None = None,
-                 groups: tuple[int, int] | None = None, shared_size: int = 0):
+                 groups: tuple[int, int] | None = None, shared_size: int = 0, gated: bool = True,
+                 group_top: int = 1):
         if not 1 <= top_k <= min(num_experts, 16):
             raise ValueError(f"top-{top_k} of {num_experts} experts: the router takes 1..min(experts, 16)")
         if num_experts > 256:
             raise ValueError(f"{num_experts} experts: the router takes at most 256")
-        if router not in ("sigmoid", "softmax_chosen", "softmax_grouped"):
-            raise ValueError(f"unknown router '{router}' (sigmoid, softmax_chosen, softmax_grouped)")
+        if router not in ("sigmoid", "softmax_chosen", "softmax_grouped", "sigmoid_grouped"):
+            raise ValueError(f"unknown router '{router}' (sigmoid, softmax_chosen, softmax_grouped, sigmoid_grouped)")
         self.groups = None
-        if router == "softmax_grouped":
+        self.group_top = int(group_top)
+        if not 1 <= self.group_top <= 15:
+            raise ValueError(f"a group is ranked by its 1..15 best scores, got {group_top}")
+        self.gated = bool(gated)
+        if router in ("softmax_grouped", "sigmoid_grouped"):
             count, keep = (int(groups[0]), int(groups[1])) if groups is not None else (1, 1)
             if not (1 <= keep <= count <= 255 and num_experts % count == 0 and keep * (num_experts // count) >= top_k):
                 raise ValueError(f"{keep} of {count} groups over {num_experts} experts cannot give {top_k} choices")
             self.groups = (count, keep)
         elif groups is not None:
-            raise ValueError("groups of experts go with the softmax_grouped router")
-        if activation not in _ACTIVATIONS:
-            raise ValueError(f"unknown expert activation '{activation}' ({', '.join(sorted(_ACTIVATIONS))})")
+            raise ValueError("groups of experts go with the softmax_grouped and sigmoid_grouped routers")
+        known = _ACTIVATIONS if self.gated else kernels.PLAIN_ACTIVATIONS
+        if activation not in known:
+            raise ValueError(f"unknown expert activation '{activation}' ({', '.join(sorted(known))})")
+        if not self.gated and shared_size:
+            raise NotImplementedError("a shared expert beside experts without a gate")
         if activation == "clamped_sigmoid" and not limit > 0:
             raise ValueError(f"the clamped activation needs a positive limit, got {limit}")
         self.D, self.E, self.k, self.Fe = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
         self.norm_topk, self.use_bias, self.scaling = bool(norm_topk), bool(use_bias), float(scaling)
         self.bias_std = float(bias_std)
-        self.router, self.act = router, _ACTIVATIONS[activation]
+        self.router, self.act = router, known[activation]
         self.limit, self.alpha = float(limit), float(alpha)
         self.n = {"router": "gate.weight", "bias": "expert_bias", "gate": "experts.{e}.w1.weight",
                   "up": "experts.{e}.w3.weight", "down": "experts.{e}.w2.weight"}
@@ -154,7 +199,8 @@ class SigmoidTopKMoE(FeedForward):
         if self.use_bias:
             t[n["bias"]] = TensorSpec((self.E,), BIAS, std=self.bias_std)
         for e in range(self.E):
-            t[n["gate"].format(e=e)] = TensorSpec((self.Fe, self.D), MATRIX)
+            if self.gated:
+                t[n["gate"].format(e=e)] = TensorSpec((self.Fe, self.D), MATRIX)
             t[n["up"].format(e=e)] = TensorSpec((self.Fe, self.D), MATRIX)
             t[n["down"].format(e=e)] = TensorSpec((self.D, self.Fe), MATRIX)
         return t
@@ -163,10 +209,15 @@ class SigmoidTopKMoE(FeedForward):
         n = self.n
         # the products' gated epilogue knows silu, gelu and the clamped form with the slope 1.702 and a limit
         # that bfloat16 holds exactly; anything else runs as a kernel of its own on the float gate and up values
-        self.epilogue = kernels.gated_epilogue(self.act, self.limit, self.alpha)
-        self.fused = (not env.is_float32) and self.Fe % 16 == 0 and self.D % 8 == 0 and self.epilogue is not None
         self.router_w = tensors[n["router"]].contiguous()
         self.router_b = tensors[n["bias"]].contiguous() if self.use_bias else None
+        if not self.gated:
+            self.epilogue, self.fused = None, False
+            self.w13 = torch.stack([tensors[n["up"].format(e=e)] for e in range(self.E)]).contiguous()
+            self.w2 = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.E)]).contiguous()
+            return
+        self.epilogue = kernels.gated_epilogue(self.act, self.limit, self.alpha)
+        self.fused = (not env.is_float32) and self.Fe % 16 == 0 and self.D % 8 == 0 and self.epilogue is not None
         self.w13 = torch.stack([fuse_gate_up(tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)],
                                              self.fused) for e in range(self.E)]).contiguous()
         self.w2 = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.E)]).contiguous()
@@ -175,7 +226,8 @@ class SigmoidTopKMoE(FeedForward):
 
     def flops_per_row(self) -> int:
         # the router, k experts of three matrices, and the shared expert
-        return 2 * self.D * self.E + self.k * 6 * self.D * self.Fe + (self.shared.flops_per_row() if self.shared else 0)
+        return 2 * self.D * self.E + self.k * (6 if self.gated else 4) * self.D * self.Fe \
+            + (self.shared.flops_per_row() if self.shared else 0)
 
     def unread_weight_bytes(self, rows: int) -> float:
         """With uniform routing an expert is chosen by none of `rows` rows with probability (1 - k/E)^rows."""
@@ -191,7 +243,9 @@ class SigmoidTopKMoE(FeedForward):
         ids = ws.get("moe.ids", (M, self.k), torch.int32)
         wts = ws.get("moe.w", (M, self.k), torch.float32)
         kernels.moe_router(ids, wts, h, self.router_w, self.router_b, self.norm_topk, self.scaling,
-                           softmax_chosen=self.router == "softmax_chosen", softmax_groups=self.groups)
+                           softmax_chosen=self.router == "softmax_chosen",
+                           softmax_groups=self.groups if self.router == "softmax_grouped" else None,
+                           sigmoid_groups=(*self.groups, self.group_top) if self.router == "sigmoid_grouped" else None)
         offsets = ws.get("moe.offsets", (self.E + 1,), torch.int32)
         sorted_pair = ws.get("moe.sorted", (P,), torch.int32)
         pair_row = ws.get("moe.rows", (P,), torch.int32)
@@ -199,7 +253,11 @@ class SigmoidTopKMoE(FeedForward):
         xs = ws.get("moe.xs", (P, self.D), env.dtype)
         kernels.gather_rows(xs, h, sorted_pair, div=self.k)
         a = ws.get("moe.a", (P, self.Fe), env.dtype)
-        if self.fused:
+        if not self.gated:
+            u = ws.get("moe.gu", (P, self.Fe), torch.float32)
+            kernels.linear(u, xs, self.w13, group_offsets=offsets, rows_hint=P)
+            kernels.activation(a, u, self.act)
+        elif self.fused:
             kernels.linear(a, xs, self.w13, self.epilogue, group_offsets=offsets, rows_hint=P)
         else:
             gu = ws.get("moe.gu", (P, 2 * self.Fe), torch.float32)

@@ -1,6 +1,7 @@
 """Rotary position encoding: the table of inverse frequencies and the pairing style.
 
-angle(pos, i) = pos * theta^(-2i/rope_dim) / factor[i], i < rope_dim/2; pairs (i, i + rope_dim/2)
+angle(pos, i) = pos * theta^(-2i/rope_dim) / factor[i] / scaling_factor, i < rope_dim/2 (`scaling_factor`: linear
+position scaling, one constant for every frequency; 1 by default); pairs (i, i + rope_dim/2)
 in the split-half ("neox") style the reference uses for this architecture, or (2i, 2i+1) in the
 adjacent style of its other dense architecture (src/dense.rs:103-111, :77).  The factors are the
 model's optional `rope_freqs.weight`, which the reference applies on layers without a window only
@@ -19,13 +20,17 @@ FREQ_FACTORS = "rope_freqs.weight"     # one tensor for the whole model
 
 @POSITION_ENCODINGS.register("rope")
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, rope_dim: int, theta: float, style: str = "neox", freq_factors: bool = False):
+    def __init__(self, rope_dim: int, theta: float, style: str = "neox", freq_factors: bool = False,
+                 scaling_factor: float = 1.0):
         if rope_dim % 2 != 0 or rope_dim < 2:
             raise ValueError(f"rope_dim must be even and positive, got {rope_dim}")
         if style not in ("neox", "adjacent"):
             raise ValueError(f"unknown rotary pairing '{style}' (neox, adjacent)")
         self.rope_dim = int(rope_dim)
         self.theta = float(theta)
+        if not float(scaling_factor) > 0:
+            raise ValueError(f"the rotation's scaling factor must be positive, got {scaling_factor}")
+        self.scaling_factor = float(scaling_factor)
         self.neox = style == "neox"
         self.freq_factors = bool(freq_factors)     # takes the model's frequency factors when the checkpoint has them
         self.inv_freq: torch.Tensor | None = None
@@ -41,6 +46,8 @@ class RotaryEncoding(PositionEncoding):
         ff = tensors.get(FREQ_FACTORS) if self.freq_factors else None
         if ff is not None:
             inv = inv / ff.detach().to("cpu", torch.float64).reshape(-1)
+        if self.scaling_factor != 1.0:
+            inv = inv / self.scaling_factor
         self.inv_freq = inv.to(torch.float32).to(env.device)
 
     def fused_rotary(self):
