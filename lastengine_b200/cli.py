@@ -119,14 +119,18 @@ def cmd_dense_cmp(a) -> int:
 
 def cmd_inspect(a) -> int:
     from .config.base import architecture_name, read_config_json
-    from .registry import plan_from_config
+    from .registry import MIXERS, plan_from_config
     from .weights.safetensors_io import open_checkpoint
     raw = read_config_json(a.path)
     plan = plan_from_config(raw)
     print(f"architecture {architecture_name(raw)}: {len(plan.layers)} layers, hidden {plan.hidden_size}, "
           f"vocab {plan.vocab_size}")
+    def kind_of(spec) -> str:
+        inner = [v.kind for v in spec.params.values() if hasattr(v, "kind") and hasattr(v, "params") and v.kind in MIXERS]
+        return f"{spec.kind} ({' | '.join(inner)})" if inner else spec.kind      # a mixer made of mixers names them
+
     for i, l in enumerate(plan.layers):
-        print(f"  layer {i}: {l.mixer.kind} + {l.ffn.kind if l.ffn is not None else 'no feed-forward'}")
+        print(f"  layer {i}: {kind_of(l.mixer)} + {l.ffn.kind if l.ffn is not None else 'no feed-forward'}")
     order = [e.layer for e in plan.schedule]
     if order != list(range(len(plan.layers))):
         print(f"  layers run in the order {' '.join(map(str, order))}")

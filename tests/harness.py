@@ -198,3 +198,105 @@ def run_batch(eng, requests, prompt_lens, keep=to_host) -> list[torch.Tensor]:
         for s in seqs:
             if s is not None:
                 eng.release(s)
+
+
+# ---- a part alone on the GPU: its own cache, steps laid out as the engine lays them out -------------------
+def bf16_round_np(a: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(np.asarray(a, dtype=np.float64)).to(torch.bfloat16).double().numpy()
+
+
+def max_err(got, want) -> float:
+    """max |got - want| / max |want|."""
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    return float(np.abs(got - want).max() / np.abs(want).max())
+
+
+def random_rows(T: int, D: int, seed: int, bf16: bool, scale: float = 1.0) -> np.ndarray:
+    h = np.random.default_rng(seed).standard_normal((T, D)) * scale
+    return bf16_round_np(h) if bf16 else h
+
+
+class MixerRig:
+    """A mixer of the registry with random weights (kept in double precision in `plain`, by the part's tensor
+    names) and a cache of its own."""
+
+    def __init__(self, kind, params, dtype: str, seed=0, std=0.3, max_tokens=2048, max_seqs=6, edit=None, device="cuda:0",
+                 hidden_size=None):
+        from lastengine_b200.cache import Cache
+        from lastengine_b200.engine.batch import BatchBuilder
+        from lastengine_b200.engine.workspace import Workspace
+        from lastengine_b200.parts.base import BuildEnv
+        from lastengine_b200.registry import MIXERS
+        from lastengine_b200.weights.loader import kept_dtype
+        from lastengine_b200.weights.random_init import random_tensor
+        dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+        dev = torch.device(device)
+        self.device = device
+        self.env = BuildEnv(device=dev, dtype=dt, workspace=Workspace(dev))
+        self.mixer = MIXERS.get(kind)(**params)
+        specs = self.mixer.tensors()
+        self.plain = {}
+        for name, spec in specs.items():
+            t = random_tensor(name, spec, seed, std, norm_init="random").to(torch.bfloat16).double()
+            self.plain[name] = t.numpy().copy()
+        if edit:
+            edit(self.plain)
+            self.plain = {n: bf16_round_np(v) for n, v in self.plain.items()}
+        self.mixer.load({n: torch.from_numpy(v).float().to(dev, kept_dtype(specs[n], torch.bfloat16, dt))
+                         for n, v in self.plain.items()}, self.env)
+        self.cache = Cache({0: self.mixer.cache_spec()}, max_tokens=max_tokens, max_seqs=max_seqs, dtype=dt, device=dev)
+        self.builder = BatchBuilder(dev)
+        self.D = params["hidden_size"] if hidden_size is None else hidden_size
+
+    def step(self, slots, hs):
+        """hs: per sequence a [n, D] array of mixer inputs; returns the mixer's outputs per sequence."""
+        from lastengine_b200.cache import pooled_table_key
+        from lastengine_b200.ops import kernels
+        slots = list(slots)
+        grow = {s: h.shape[0] for s, h in zip(slots, hs)}
+        pos0 = [self.cache.length(s) for s in slots]
+        self.cache.reserve(grow)
+        tables = {}
+        for gi, g in enumerate(self.cache.kv_groups):
+            tables[gi] = g.table(slots, max(1, max(len(g.seq_pages.get(s, ())) for s in slots)))
+            if g.pool > 0:
+                tables[pooled_table_key(gi)] = g.table(
+                    slots, max(1, max(len(g.seq_pooled_pages.get(s, ())) for s in slots)), pooled=True)
+        batch = self.builder.build(slots, [[0] * h.shape[0] for h in hs], pos0, [], tables)
+        h = torch.from_numpy(np.concatenate(hs, 0)).to(self.device, self.env.dtype)
+        out = torch.zeros(h.shape[0], self.D, dtype=torch.float32, device=self.device)
+        self.mixer.forward(h, out, False, batch, self.cache.view(0, True, batch.tables), self.env)
+        kernels.check_device_status()
+        self.cache.commit(grow)
+        out = out.double().cpu().numpy()
+        return np.split(out, np.cumsum([x.shape[0] for x in hs])[:-1])
+
+    def alone(self, h):
+        s = self.cache.alloc_seq()
+        try:
+            return self.step([s], [h])[0]
+        finally:
+            self.cache.free_seq(s)
+
+
+def whole_portions_and_batches(rig: MixerRig, plain_fn, lengths, more_n, cuts, tol: float, bf16: bool, seed=10, scale=1.0):
+    """Each sequence alone and whole; then all together in the slots and pages just given back; then every
+    one goes on in portions (rows cut at `cuts`) beside the others."""
+    hs = [random_rows(n, rig.D, seed + n, bf16, scale) for n in lengths]
+    want = [plain_fn(h) for h in hs]
+    for h, w in zip(hs, want):
+        assert max_err(rig.alone(h), w) < tol, f"alone, {h.shape[0]} rows"
+    more = [random_rows(more_n, rig.D, seed + 50 + i, bf16, scale) for i in range(len(hs))]
+    want2 = [plain_fn(np.concatenate([h, x])) for h, x in zip(hs, more)]
+    slots = [rig.cache.alloc_seq() for _ in hs]
+    for g, w in zip(rig.step(slots, hs), want):
+        assert max_err(g, w) < tol, "batched"
+    outs = [[] for _ in hs]
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        for i, g in enumerate(rig.step(slots, [x[a:b] for x in more])):
+            outs[i].append(g)
+    for i, w in enumerate(want2):
+        assert max_err(np.concatenate(outs[i]), w[hs[i].shape[0]:]) < tol, f"sequence {i} after portions"
+    for s in slots:
+        rig.cache.free_seq(s)
+    rig.cache.check()

@@ -157,7 +157,7 @@ def min_gru(h, w):
 def parallel_mixer(h, w, m, eps):
     left = mixed_heads_attention(h, sub(w, "left"), m["left"], eps)
     right = min_gru(h, sub(w, "right"))
-    return m["left_scale"] * left + m["right_scale"] * right
+    return float(m.get("left_scale", 1.0)) * left + float(m.get("right_scale", 1.0)) * right
 
 
 def mlstm(h, w, m, eps):
@@ -207,7 +207,7 @@ def route(h, w, r):
     c = np.where(np.repeat(allowed, per, axis=-1), c, -np.inf)
     ids = np.argsort(-c, axis=-1, kind="stable")[:, :top]                             # ties to the lower index
     chosen = np.take_along_axis(s, ids, axis=-1)
-    wts = chosen / (chosen.sum(-1, keepdims=True) + 1e-20) * float(r["scale"])
+    wts = chosen / (chosen.sum(-1, keepdims=True) + 1e-20) * float(r.get("scale", 1.0))
     return ids, wts, c
 
 
@@ -251,9 +251,44 @@ def run_layer(x, w, spec, eps):
 def forward(cfg: dict, w: dict, tokens, streams: list | None = None) -> np.ndarray:
     """Logits [T, vocab] of one sequence; `streams` collects the stream after every layer run."""
     eps = float(cfg["norm"]["eps"])
-    x = w["embed"][np.asarray(tokens)] * float(cfg["embedding"]["scale"])
+    x = w["embed"][np.asarray(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     for li in layer_order(cfg):
         x = run_layer(x, sub(w, f"l{li}"), cfg["layers"][li], eps)
         if streams is not None:
             streams.append(x.copy())
     return layer_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def route_gap(h, w, r) -> np.ndarray:
+    """Per row, how far the router's decisions are from falling the other way: the gap between the last chosen and
+    the first rejected choice score among the eligible experts, and between the last kept and the first dropped group."""
+    E, top = int(r["experts"]), int(r["top"])
+    _, _, c = route(h, w, r)
+    cs = -np.sort(-c, axis=-1)
+    gap = np.full(h.shape[0], np.inf)
+    if E > top:
+        nxt = cs[:, top]
+        gap = np.where(np.isfinite(nxt), cs[:, top - 1] - nxt, np.inf)
+    groups = r.get("groups") or {}
+    count, keep = int(groups.get("count", 1)), int(groups.get("keep", 1))
+    if keep < count:
+        per = E // count
+        c0 = sigmoid(h @ w["router"].T) + w["correction"]
+        rank = np.sort(c0.reshape(-1, count, per), axis=-1)[..., -2:].sum(-1) if per >= 2 else c0.reshape(-1, count, per).sum(-1)
+        rs = -np.sort(-rank, axis=-1)
+        gap = np.minimum(gap, rs[:, keep - 1] - rs[:, keep])
+    return gap
+
+
+def router_gaps(cfg: dict, w: dict, tokens) -> np.ndarray:
+    """Per position the smallest routing gap over the model's layer runs (inf without experts)."""
+    eps = float(cfg["norm"]["eps"])
+    x = w["embed"][np.asarray(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
+    gap = np.full(len(tokens), np.inf)
+    for li in layer_order(cfg):
+        spec, lw = cfg["layers"][li], sub(w, f"l{li}")
+        mlp = spec.get("mlp")
+        if mlp is not None and mlp["kind"] == "moe":
+            gap = np.minimum(gap, route_gap(layer_norm(x, lw["norm2"], eps), sub(lw, "mlp"), mlp["router"]))
+        x = run_layer(x, lw, spec, eps)
+    return gap

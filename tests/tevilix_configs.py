@@ -1,0 +1,90 @@
+"""Small Tevilix configurations for the tests.  They differ from one another in every size and constant: width,
+vocabulary, eps, embedding scale, the order of the layers and the looped range (none, one layer, several, all),
+which layers have a feed-forward and of which kind, head counts and grouping (one key head for all heads, a key
+head per head), key and value sizes (equal, smaller, larger, no multiples of 8), the rotated part of a head
+(none, part, all), the positions' scaling (also 1), windows (one position, a few, more than a cache page, none),
+the side-by-side weights (also 1), recurrent widths, the gates' cap, expert counts, choices and groups (none,
+some kept, all kept, groups of one expert)."""
+
+
+def att(heads, kv_heads, dim, vdim, scale, rot_dims, base, factor, size):
+    a = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot_dims is not None:
+        a["rot"] = {"dims": rot_dims, "base": base}
+        if factor is not None:
+            a["rot"]["scaling"] = {"factor": factor}
+    if size:
+        a["mask"] = {"size": size}
+    return a
+
+
+def par(left, left_scale, width, right_scale):
+    return {"left": left, "left_scale": left_scale, "right": {"width": width}, "right_scale": right_scale}
+
+
+def mls(heads, dim, vdim, cap):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(experts, top, count, keep, scale, ff):
+    r = {"experts": experts, "top": top, "scale": scale}
+    if count:
+        r["groups"] = {"count": count, "keep": keep}
+    return {"kind": "moe", "router": r, "expert": {"ff": ff}}
+
+
+def layer(kind, mixer, mlp):
+    return {"type": kind, "mixer": mixer, "mlp": mlp}
+
+
+# the matrix memory first; two layers looped twice; three heads on a key head; a window shorter than a page
+T_A = {
+    "architecture": "Tevilix", "vocab": 200, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0},
+    "layers": [
+        layer("mlstm", mls(4, 16, 24, 8.0), dense(96)),
+        layer("parallel", par(att(6, 2, 32, 16, 0.2, 16, 10000.0, 4.0, 20), 0.7, 48, 1.3), moe(8, 2, 4, 2, 1.5, 32)),
+        layer("mlstm", mls(2, 64, 32, 15.0), None),
+        layer("parallel", par(att(2, 1, 16, 48, 0.3, 16, 1000.0, None, 33), 1.0, 80, 1.0), moe(6, 3, None, None, 1.0, 24)),
+    ],
+    "loop": {"start": 1, "stop": 3, "times": 2},
+}
+
+# heads of 64 and 128, a window longer than a page, every layer looped, one choice of many, groups of one expert
+T_B = {
+    "architecture": "Tevilix", "vocab": 150, "width": 72, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+    "layers": [
+        layer("parallel", par(att(3, 3, 64, 64, 0.125, 64, 200000.0, 1.0, 70), 1.2, 40, 0.5), moe(12, 1, 3, 1, 2.0, 16)),
+        layer("mlstm", mls(3, 32, 64, 10.0), moe(4, 2, 4, 3, 0.5, 40)),
+        layer("parallel", par(att(4, 1, 128, 128, 0.09, 32, 1e6, 8.0, 9), 0.9, 72, 0.9), dense(48)),
+    ],
+    "loop": {"start": 0, "stop": 3, "times": 2},
+}
+
+# sizes that are no multiple of 8, no rotation in one layer, a window of one position, no loop, no window in one layer
+T_C = {
+    "architecture": "Tevilix", "vocab": 97, "width": 40, "norm": {"eps": 1e-4},
+    "layers": [
+        layer("parallel", par(att(5, 5, 12, 20, 0.25, None, None, None, 1), 1.0, 25, 2.0), dense(56)),
+        layer("mlstm", mls(5, 10, 6, 12.0), None),
+        layer("parallel", par(att(2, 2, 24, 10, 0.4, 0, 10000.0, 2.0, 0), 0.6, 33, 1.1), moe(9, 2, 3, 2, 2.5, 14)),
+        layer("mlstm", mls(1, 40, 40, 5.0), moe(5, 5, 1, 1, 1.0, 8)),
+        layer("parallel", par(att(3, 1, 40, 24, 0.1, 40, 20000.0, 1.5, 64), 1.5, 16, 0.3), dense(24)),
+    ],
+}
+
+# larger states, one layer run three times, eight heads, a window of two pages
+T_D = {
+    "architecture": "Tevilix", "vocab": 320, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 9.5},
+    "layers": [
+        layer("parallel", par(att(8, 4, 64, 32, 0.15, 32, 50000.0, 2.0, 128), 0.8, 200, 1.1), moe(16, 4, 4, 1, 2.5, 24)),
+        layer("mlstm", mls(3, 128, 64, 12.0), dense(80)),
+        layer("mlstm", mls(6, 32, 16, 20.0), moe(10, 3, 5, 3, 1.0, 16)),
+    ],
+    "loop": {"start": 1, "stop": 2, "times": 3},
+}
+
+ALL = {"A": T_A, "B": T_B, "C": T_C, "D": T_D}
