@@ -25,7 +25,7 @@ A step is one decode step of the whole batch.  One JSON line goes to stdout:
 
 Weights (1.8 GB) are far larger than L2, so consecutive steps cannot be served from L2.
 
-`--compare zekivik` (or `lenesun`) leaves all of that aside and prints a line of its own: prompt and decode times
+`--compare zekivik` (or `lenesun`, `kisilix`, `tevilix`) leaves all of that aside and prints a line of its own: prompt and decode times
 of that design at a few layer sizes beside the closest LFM3 model at equal sizes, with every kernel entry point's time.
 """
 from __future__ import annotations
@@ -472,6 +472,52 @@ def _kisilix_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict
     return {"bytes": by, "flops": fl}
 
 
+# ---- the Tevilix design beside the Kisilix design at equal layer sizes (--compare tevilix) ----------------
+def tevilix_config(width: int, ff: int, heads: int, kv_heads: int, dim: int, vdim: int, ret_heads: int, ret_dim: int,
+                   ret_vdim: int, layers: int, vocab: int, window: int, pool: int = 0) -> dict:
+    """Side-by-side layers (windowed attention with mixed heads beside the minimal recurrent unit, as wide as the
+    model) alternate with the matrix memory with exponential gates; every layer has the dense feed-forward.  The
+    attention takes the other design's head sizes and window, the matrix memory its recurrent layers' sizes."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+           "rot": {"dims": dim, "base": 1000000.0, "scaling": {"factor": 2.0}}, "mask": {"size": window}}
+    par = {"left": att, "left_scale": 0.8, "right": {"width": width}, "right_scale": 1.1}
+    mem = {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim, "gate_cap": 12.0}
+    ls = [{"type": "mlstm" if i % 2 else "parallel", "mixer": mem if i % 2 else par, "mlp": {"kind": "dense", "ff": ff}}
+          for i in range(layers)]
+    return {"architecture": "Tevilix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": ls}
+
+
+def _tevilix_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict:
+    """What a step's launches of the design's own kernels have to move (bytes) or compute (flops), by entry point."""
+    W = cfg["width"]
+    by = {"leb_layernorm_pair": 0, "leb_activation": 0, "leb_weighted_pair_sum": 0, "leb_pooled_attn_prep": 0,
+          "leb_attention_mixed": 0, "leb_min_gru": 0, "leb_exp_gates": 0, "leb_gated_recurrence": 0, "leb_exp_gates_finish": 0}
+    fl = {"leb_attention_mixed": 0, "leb_gated_recurrence": 0}
+    per_seq = rows // batch
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        by["leb_layernorm_pair"] += rows * W * (4 + 4 + 4 + 2 + 2)                    # x and y read, x written, two norms written
+        if l["mlp"]:
+            by["leb_activation"] += rows * l["mlp"]["ff"] * (4 + 2)
+        if l["type"] == "parallel":
+            a = m["left"]
+            nh, nkv, hd, vd, win = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["mask"]["size"]
+            by["leb_weighted_pair_sum"] += rows * W * 12
+            by["leb_pooled_attn_prep"] += rows * ((nh + nkv) * hd + nkv * vd) * (4 + 2)
+            seen = sum(min(i + 1, win) for i in range(context - per_seq, context))
+            fl["leb_attention_mixed"] += 2 * nh * (hd + vd + nh) * seen * batch
+            by["leb_attention_mixed"] += batch * min(context, win) * nkv * (hd + vd) * 2 + rows * nh * (hd + 3 * vd) * 2
+            by["leb_min_gru"] += rows * m["right"]["width"] * (12 + 2) + batch * m["right"]["width"] * 8
+        else:
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            by["leb_exp_gates"] += rows * H * 5 * 4
+            by["leb_gated_recurrence"] += rows * (2 * H * d + 2 * H * e + 2 * H) * 4 + batch * H * d * (e + 1) * 8
+            fl["leb_gated_recurrence"] += rows * H * d * (e + 1) * 6
+            by["leb_exp_gates_finish"] += rows * H * e * (4 + 4 + 2)
+    return {"bytes": by, "flops": fl}
+
+
 def compare_designs(which: str, steps: int, warmup: int) -> int:
     import numpy as np
     import torch
@@ -480,9 +526,13 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
     results = {}
-    other = "zekivik" if which == "kisilix" else "lfm3"
-    for size_name, sz in {"zekivik": COMPARE_SIZES, "lenesun": LENESUN_SIZES, "kisilix": KISILIX_SIZES}[which].items():
-        if which == "kisilix":
+    other = "zekivik" if which == "kisilix" else ("kisilix" if which == "tevilix" else "lfm3")
+    for size_name, sz in {"zekivik": COMPARE_SIZES, "lenesun": LENESUN_SIZES, "kisilix": KISILIX_SIZES,
+                          "tevilix": KISILIX_SIZES}[which].items():
+        if which == "tevilix":
+            zc = tevilix_config(vocab=32768, **sz)
+            lc = kisilix_config(vocab=32768, **sz)
+        elif which == "kisilix":
             zc = kisilix_config(vocab=32768, **sz)
             lc = zekivik_config(vocab=32768, loop=False, **{k: v for k, v in sz.items() if k not in ("window", "pool")})
         elif which == "zekivik":
@@ -500,7 +550,12 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             print(f"[bench] {size_name} {label}: {r['weights_gb']} GB of weights", file=sys.stderr, flush=True)
             pre_ms = time_prefill(eng, PREFILL_TOKENS, 3, 5, rng)
             print(f"[bench] {size_name} {label}: prompt of {PREFILL_TOKENS} tokens {pre_ms:.3f} ms", file=sys.stderr, flush=True)
-            if label == "kisilix":      # a position sees its window and the pooled blocks behind it, not every earlier one
+            if label == "tevilix":      # a position sees its window
+                attn_flops = _tevilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS)["flops"]["leb_attention_mixed"]
+                kv_seen = [sum(min(2048, l["mixer"]["left"]["mask"]["size"]) * l["mixer"]["left"]["kv_heads"]
+                               * (l["mixer"]["left"]["dim"] + l["mixer"]["left"]["vdim"]) * 2
+                               for l in cfg["layers"] if l["type"] == "parallel")]
+            elif label == "kisilix":      # a position sees its window and the pooled blocks behind it, not every earlier one
                 attn_flops = _kisilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS)["flops"]["leb_attention_pooled"]
                 kv_seen = [sum(_seen_keys(2047, l["mixer"]["mask"]["size"], l["mixer"]["mask"]["pool"]) * l["mixer"]["kv_heads"]
                                * (l["mixer"]["dim"] + l["mixer"]["vdim"]) * 2 for l in cfg["layers"] if l["type"] == "attention")]
@@ -539,8 +594,12 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             eng.release(seqs)
             dec_k = t.summary()
             by, fl = {}, {}
-            if label == "kisilix":
-                wp, wd = _kisilix_kernel_work(zc, PREFILL_TOKENS, 1, PREFILL_TOKENS), _kisilix_kernel_work(zc, 8, 8, 2048)
+            if label == "tevilix":
+                wp, wd = _tevilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS), _tevilix_kernel_work(cfg, 8, 8, 2048)
+                by = {"prefill": wp["bytes"], "decode_b8": wd["bytes"]}
+                fl = {"prefill": wp["flops"]}
+            elif label == "kisilix":
+                wp, wd = _kisilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS), _kisilix_kernel_work(cfg, 8, 8, 2048)
                 by = {"prefill": wp["bytes"], "decode_b8": wd["bytes"]}
                 fl = {"prefill": wp["flops"]}
             elif label == "zekivik":
@@ -580,6 +639,7 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             torch.cuda.empty_cache()
         results[size_name] = {"sizes": sz, **row}
     against = {"zekivik": "lfm3 hybrid at equal layer sizes", "kisilix": "zekivik hybrid at equal layer sizes",
+               "tevilix": "kisilix at equal layer sizes",
                "lenesun": "lfm3 with attention and experts in every layer at equal layer sizes"}[which]
     print(json.dumps({"compare": which, "against": against, "dtype": "bf16",
                       "data": "synthetic (random weights, uniform random token ids)", "peaks": pk_src,
@@ -606,7 +666,7 @@ def main() -> int:
     ap.add_argument("--unequal", type=int, default=0, metavar="N",
                     help="instead of the default run: N requests with prompts of U[64, 2048] tokens generate "
                          "--steps tokens each in one batch through the Python entry point (prints its own JSON line)")
-    ap.add_argument("--compare", default="", choices=["", "zekivik", "lenesun", "kisilix"],
+    ap.add_argument("--compare", default="", choices=["", "zekivik", "lenesun", "kisilix", "tevilix"],
                     help="instead of the default run: prefill and decode of that design at a few layer sizes beside "
                          "the closest other design at equal sizes, with every kernel's time (prints its own JSON line)")
     args = ap.parse_args()

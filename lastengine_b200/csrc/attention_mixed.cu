@@ -344,6 +344,330 @@ attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part
   }
 }
 
+// ---- prompts in bfloat16 on the tensor cores ---------------------------------------------------------------
+// The same attention for the many rows of a prompt.  A block of 16 warps takes 16 query rows of one sequence and
+// ALL heads, and walks the key range in tiles of 32 keys:
+//   1. the tile's keys of every kv head go to shared memory; every warp forms raw score tiles S_g = Q_g K^T
+//      (16 rows x 8 keys, mma.sync m16n8k16, bfloat16 operands, float sums) for its share of the (head, 8 keys)
+//      pairs and leaves them, times the scale, in shared memory as floats;
+//   2. warp i takes row i with a lane per key: it reads the row's raw scores of all heads once, mixes them into
+//      every head's score with the [heads, heads] matrix (float multiply-adds, the matrix transposed in shared
+//      memory so that four heads' factors are one load), masks, and runs the streaming softmax of every head
+//      (lane h keeps head h's running maximum and sum); the weights go back over the row's raw scores as two
+//      bfloat16 terms, hi = bf16(p) and lo = bf16(p - hi), so that the product with the values sees 16
+//      significant bits of p; meanwhile the tile's values arrive in the buffer the keys have left;
+//   3. every warp adds P V for its share of the (head, 8 value dimensions) pairs (two products, hi and lo),
+//      after scaling its sums by the factor the softmax left for (head, row).
+// Float everywhere outside the products' operands.  Sizes: up to 32 heads, key heads in multiples of 16 numbers,
+// value heads in multiples of 8, heads x value size up to 2,048 (a thread then holds 64 sums).
+constexpr int AMM_ROWS = 16, AMM_KT = 32, AMM_WARPS = 16, AMM_SLOT = 36;
+
+__device__ __forceinline__ void amm_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Shared memory: talkT [H][HP] floats | corr [H][16] floats | raw / P [H][16][AMM_SLOT] floats (a row's 32 raw
+// scores, later its weights: hi in the first 16 words, lo in the next 16) | q [H][16][hd + 8] bfloat16 |
+// keys [G][32][hd + 8] or values [G][vd][40] bfloat16 (one buffer).
+template <int HP, int UPW>
+__global__ void __launch_bounds__(32 * AMM_WARPS, 1)
+attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ k_pool,
+                           const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int bt_width,
+                           const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
+                           const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
+                           const float* __restrict__ talk, const float* __restrict__ gate, int ldg, int H, int G, int hd,
+                           int vd, int page_size, int window, float scale) {
+  extern __shared__ __align__(16) unsigned char amm_sm[];
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int b = blockIdx.y;
+  const int slot = seq_slot[b];
+  const int qlen = seq_qlen ? seq_qlen[b] : 1;
+  const int row_lo = blockIdx.x * AMM_ROWS;
+  if (row_lo >= qlen) return;
+  const int nrows = min(AMM_ROWS, qlen - row_lo);
+  const int q0 = seq_qstart[b], pos0 = seq_pos0[b];
+  const int Gq = H / G;
+  const int QS = hd + 8, KS = hd + 8, VS = AMM_KT + 8;
+  const int n_dt = vd / 8;                       // tiles of 8 value dimensions in a head
+  const int n_units = H * n_dt;                  // (head, dimension tile) pairs of the block
+
+  float* talkT = reinterpret_cast<float*>(amm_sm);            // [g][HP]
+  float* corr_s = talkT + H * HP;                             // [h][16]
+  float* raw_s = corr_s + H * AMM_ROWS;                       // [h][16][AMM_SLOT]
+  bf16* q_s = reinterpret_cast<bf16*>(raw_s + (size_t)H * AMM_ROWS * AMM_SLOT);   // [g][16][QS]
+  bf16* kv_s = q_s + (size_t)H * AMM_ROWS * QS;
+
+  if (slot < 0) {      // a padding sequence: a defined result, no cache access
+    for (int idx = threadIdx.x; idx < nrows * H * vd; idx += blockDim.x)
+      out[(size_t)(q0 + row_lo) * H * vd + idx] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  for (int idx = threadIdx.x; idx < H * HP; idx += blockDim.x) {
+    const int g = idx / HP, h = idx - g * HP;
+    talkT[idx] = h < H ? talk[h * H + g] : 0.f;
+  }
+  {      // queries: [g][i][hd] with zero rows beyond the block's rows, 16 bytes at a time
+    const int per_row = hd / 8, total = H * AMM_ROWS * per_row;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+      const int g = idx / (AMM_ROWS * per_row), rest = idx - g * (AMM_ROWS * per_row);
+      const int i = rest / per_row, d0 = (rest - i * per_row) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (i < nrows) v = *reinterpret_cast<const uint4*>(q + (size_t)(q0 + row_lo + i) * ldq + (size_t)g * hd + d0);
+      *reinterpret_cast<uint4*>(q_s + ((size_t)g * AMM_ROWS + i) * QS + d0) = v;
+    }
+  }
+  const int kv_len = pos0 + qlen;
+  const int pos_lo = pos0 + row_lo, pos_hi = pos_lo + nrows - 1;
+  const int key_lo = (window > 0 && pos_lo + 1 > window) ? pos_lo + 1 - window : 0;
+  const int tile_first = key_lo / AMM_KT, n_tiles = pos_hi / AMM_KT - tile_first + 1;
+
+  float acc[UPW][4];
+#pragma unroll
+  for (int u = 0; u < UPW; u++)
+#pragma unroll
+    for (int x = 0; x < 4; x++) acc[u][x] = 0.f;
+  float m_run = AMX_NEG, l_run = 0.f;      // of head `lane` and row `warp`
+
+  for (int ut = 0; ut < n_tiles; ut++) {
+    const int key0 = (tile_first + ut) * AMM_KT;
+    const int page = block_table[(size_t)b * bt_width + key0 / page_size];
+    const int in_page = key0 % page_size;
+    __syncthreads();      // the buffer is free (the values of the tile before are used up); q and talkT are in place
+    {      // keys [c][j][hd]
+      const int per_row = hd / 8, total = G * AMM_KT * per_row;
+      for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int c = idx / (AMM_KT * per_row), rest = idx - c * (AMM_KT * per_row);
+        const int j = rest / per_row, d0 = (rest - j * per_row) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (page >= 0 && key0 + j < kv_len)
+          v = *reinterpret_cast<const uint4*>(k_pool + (((size_t)page * G + c) * page_size + in_page + j) * hd + d0);
+        *reinterpret_cast<uint4*>(kv_s + ((size_t)c * AMM_KT + j) * KS + d0) = v;
+      }
+    }
+    __syncthreads();
+    // 1. raw scores: units (head g, 8 keys nt)
+    for (int u = warp; u < H * (AMM_KT / 8); u += AMM_WARPS) {
+      const int g = u / (AMM_KT / 8), nt = u - g * (AMM_KT / 8);
+      const bf16* qa = q_s + (size_t)g * AMM_ROWS * QS;
+      const bf16* kb = kv_s + ((size_t)(g / Gq) * AMM_KT + nt * 8 + gid) * KS;
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int k0 = 0; k0 < hd; k0 += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(qa + (size_t)gid * QS + k0 + 2 * tig);
+        a[1] = *reinterpret_cast<const uint32_t*>(qa + (size_t)(gid + 8) * QS + k0 + 2 * tig);
+        a[2] = *reinterpret_cast<const uint32_t*>(qa + (size_t)gid * QS + k0 + 8 + 2 * tig);
+        a[3] = *reinterpret_cast<const uint32_t*>(qa + (size_t)(gid + 8) * QS + k0 + 8 + 2 * tig);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + k0 + 2 * tig);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + k0 + 8 + 2 * tig);
+        amm_mma(d, a, b0, b1);
+      }
+      float* r0 = raw_s + ((size_t)g * AMM_ROWS + gid) * AMM_SLOT + nt * 8 + 2 * tig;
+      float* r1 = raw_s + ((size_t)g * AMM_ROWS + gid + 8) * AMM_SLOT + nt * 8 + 2 * tig;
+      r0[0] = d[0] * scale;
+      r0[1] = d[1] * scale;
+      r1[0] = d[2] * scale;
+      r1[1] = d[3] * scale;
+    }
+    __syncthreads();      // the scores are complete; the keys are used up
+    // the tile's values on their way: asked for now, stored after the softmax
+    constexpr int VPT = 4;      // 16-byte pieces of the values a thread takes (G * vd * 4 pieces in all)
+    uint4 vreg[VPT];
+    const int v_total = G * vd * (AMM_KT / 8);
+#pragma unroll
+    for (int x = 0; x < VPT; x++) {
+      const int idx = threadIdx.x + x * blockDim.x;
+      vreg[x] = make_uint4(0, 0, 0, 0);
+      if (idx < v_total && page >= 0) {
+        const int cd = idx / (AMM_KT / 8), ch = idx - cd * (AMM_KT / 8);      // cd = c * vd + d
+        vreg[x] = *reinterpret_cast<const uint4*>(v_pool + ((size_t)page * G * vd + cd) * page_size + in_page + ch * 8);
+      }
+    }
+    // 2. row `warp`: mix the heads' scores, mask, streaming softmax of every head, weights as two bfloat16 terms
+    {
+      const int i = warp;
+      const int pos = pos_lo + i, key = key0 + lane;
+      const bool seen = i < nrows && key <= pos && (window <= 0 || pos - key < window);
+      float t[HP];
+#pragma unroll
+      for (int h = 0; h < HP; h++) t[h] = 0.f;
+      for (int g = 0; g < H; g++) {
+        const float r = raw_s[((size_t)g * AMM_ROWS + i) * AMM_SLOT + lane];
+        const float4* tk = reinterpret_cast<const float4*>(talkT + g * HP);
+#pragma unroll
+        for (int h4 = 0; h4 < HP / 4; h4++) {
+          const float4 w4 = tk[h4];
+          t[4 * h4 + 0] = fmaf(w4.x, r, t[4 * h4 + 0]);
+          t[4 * h4 + 1] = fmaf(w4.y, r, t[4 * h4 + 1]);
+          t[4 * h4 + 2] = fmaf(w4.z, r, t[4 * h4 + 2]);
+          t[4 * h4 + 3] = fmaf(w4.w, r, t[4 * h4 + 3]);
+        }
+      }
+      __syncwarp();      // every lane has read the row's raw scores before the weights overwrite them
+#pragma unroll
+      for (int h = 0; h < HP; h++) {
+        if (h >= H) break;
+        const float tmax = warp_max(seen ? t[h] : AMX_NEG);
+        const float m_old = __shfl_sync(0xffffffffu, m_run, h);
+        const float l_old = __shfl_sync(0xffffffffu, l_run, h);
+        const float m_new = fmaxf(m_old, tmax);
+        const float w = seen ? expf(t[h] - m_new) : 0.f;
+        const float corr = expf(m_old - m_new);
+        const float l_new = l_old * corr + warp_sum(w);
+        if (lane == h) {
+          m_run = m_new;
+          l_run = l_new;
+          corr_s[h * AMM_ROWS + i] = corr;
+        }
+        const bf16 hi = __float2bfloat16_rn(w);
+        const bf16 lo = __float2bfloat16_rn(w - __bfloat162float(hi));
+        bf16* ps = reinterpret_cast<bf16*>(raw_s + ((size_t)h * AMM_ROWS + i) * AMM_SLOT);
+        ps[lane] = hi;
+        ps[32 + lane] = lo;
+      }
+    }
+    // the values [c][d][j], zero where no position is yet
+#pragma unroll
+    for (int x = 0; x < VPT; x++) {
+      const int idx = threadIdx.x + x * blockDim.x;
+      if (idx < v_total) {
+        const int cd = idx / (AMM_KT / 8), ch = idx - cd * (AMM_KT / 8);
+        uint4 v = vreg[x];
+        const int left = kv_len - (key0 + ch * 8);      // positions of this piece that exist
+        if (left < 8) {
+          bf16* e = reinterpret_cast<bf16*>(&v);
+#pragma unroll
+          for (int y = 0; y < 8; y++)
+            if (y >= left) e[y] = __float2bfloat16_rn(0.f);
+        }
+        *reinterpret_cast<uint4*>(kv_s + (size_t)cd * VS + ch * 8) = v;
+      }
+    }
+    __syncthreads();
+    // 3. weighted values: units (head h, 8 dimensions dt)
+#pragma unroll
+    for (int uu = 0; uu < UPW; uu++) {
+      const int u = warp + uu * AMM_WARPS;
+      if (u >= n_units) break;
+      const int h = u / n_dt, dt = u - h * n_dt;
+      const float c0 = corr_s[h * AMM_ROWS + gid], c1 = corr_s[h * AMM_ROWS + gid + 8];
+      acc[uu][0] *= c0;
+      acc[uu][1] *= c0;
+      acc[uu][2] *= c1;
+      acc[uu][3] *= c1;
+      const uint32_t* p0 = reinterpret_cast<const uint32_t*>(raw_s + ((size_t)h * AMM_ROWS + gid) * AMM_SLOT);
+      const uint32_t* p1 = reinterpret_cast<const uint32_t*>(raw_s + ((size_t)h * AMM_ROWS + gid + 8) * AMM_SLOT);
+      const bf16* vb = kv_s + ((size_t)(h / Gq) * vd + dt * 8 + gid) * VS;
+#pragma unroll
+      for (int k0 = 0; k0 < AMM_KT; k0 += 16) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vb + k0 + 2 * tig);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(vb + k0 + 8 + 2 * tig);
+        uint32_t a[4];
+        a[0] = p0[k0 / 2 + tig];
+        a[1] = p1[k0 / 2 + tig];
+        a[2] = p0[k0 / 2 + 4 + tig];
+        a[3] = p1[k0 / 2 + 4 + tig];
+        amm_mma(acc[uu], a, b0, b1);
+        a[0] = p0[16 + k0 / 2 + tig];
+        a[1] = p1[16 + k0 / 2 + tig];
+        a[2] = p0[16 + k0 / 2 + 4 + tig];
+        a[3] = p1[16 + k0 / 2 + 4 + tig];
+        amm_mma(acc[uu], a, b0, b1);
+      }
+    }
+  }
+  // the sums of every (head, row) to where the units' threads find them
+  __syncthreads();
+  if (lane < H) corr_s[lane * AMM_ROWS + warp] = l_run > 0.f ? 1.0f / l_run : 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int uu = 0; uu < UPW; uu++) {
+    const int u = warp + uu * AMM_WARPS;
+    if (u >= n_units) break;
+    const int h = u / n_dt, dt = u - h * n_dt;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      const int i = gid + 8 * half;
+      if (i >= nrows) continue;
+      const size_t m = (size_t)q0 + row_lo + i;
+      const float inv = corr_s[h * AMM_ROWS + i];
+      const int d = dt * 8 + 2 * tig;
+      float o0 = acc[uu][2 * half] * inv, o1 = acc[uu][2 * half + 1] * inv;
+      if (gate) {
+        const float* gp = gate + m * ldg + (size_t)h * vd + d;
+        o0 *= 1.0f / (1.0f + expf(-gp[0]));
+        o1 *= 1.0f / (1.0f + expf(-gp[1]));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(out + (m * H + h) * vd + d) = __floats2bfloat162_rn(o0, o1);
+    }
+  }
+}
+
+static size_t amm_smem(int H, int HP, int G, int hd, int vd) {
+  const size_t kv = (size_t)G * (size_t)max(AMM_KT * (hd + 8), vd * (AMM_KT + 8));
+  return sizeof(float) * ((size_t)H * HP + (size_t)H * AMM_ROWS + (size_t)H * AMM_ROWS * AMM_SLOT) +
+         2 * ((size_t)H * AMM_ROWS * (hd + 8) + kv);
+}
+
+// Whether the tensor-core kernel takes these sizes (bfloat16 prompts).
+LEB_API int leb_attention_mixed_mma_supported(int H, int G, int hd, int vd, int page_size) {
+  if (H < 1 || H > 32 || G < 1 || H % G || hd % 16 || hd < 16 || vd % 8 || vd < 8 || page_size % AMM_KT) return 0;
+  if (H * (vd / 8) > 16 * AMM_WARPS) return 0;          // a thread holds at most 16 units' sums
+  if (G * vd * (AMM_KT / 8) > 4 * 32 * AMM_WARPS) return 0;      // the values of a tile in four pieces a thread
+  const int HP = H <= 4 ? 4 : H <= 8 ? 8 : H <= 16 ? 16 : 32;
+  return amm_smem(H, HP, G, hd, vd) <= 227 * 1024 ? 1 : 0;
+}
+
+LEB_API int leb_attention_mixed_mma(void* out, const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                    const int* block_table, int bt_width, const int* seq_slot, const int* seq_pos0,
+                                    const int* seq_qstart, const int* seq_qlen, const float* talk, const float* gate, int ldg,
+                                    int M, int B, int H, int G, int hd, int vd, int page_size, int window, float scale,
+                                    int max_qlen, cudaStream_t st) {
+  if (M <= 0 || B <= 0) return 0;
+  LEB_REQUIRE(leb_attention_mixed_mma_supported(H, G, hd, vd, page_size), "leb_attention_mixed_mma: sizes %d/%d heads of %d/%d not taken", H, G, hd, vd);
+  LEB_REQUIRE(ldq % 8 == 0 && ((uintptr_t)q & 15) == 0, "leb_attention_mixed_mma: query rows must start on 16 bytes");
+  LEB_REQUIRE(B <= 65535, "leb_attention_mixed_mma: step too large");
+  const int HP = H <= 4 ? 4 : H <= 8 ? 8 : H <= 16 ? 16 : 32;
+  const size_t smem = amm_smem(H, HP, G, hd, vd);
+  const int units = H * (vd / 8);
+  int upw = ceil_div(units, AMM_WARPS);
+  upw = upw <= 1 ? 1 : upw <= 2 ? 2 : upw <= 4 ? 4 : upw <= 8 ? 8 : 16;
+  const dim3 grid(ceil_div(max_qlen, AMM_ROWS), B), block(32 * AMM_WARPS);
+  LebPlainLaunches plain(true);
+#define AMM_LAUNCH(HP_, UPW_)                                                                                              \
+  {                                                                                                                        \
+    static size_t set = 48 * 1024;                                                                                         \
+    if (smem > set) {                                                                                                      \
+      if (cudaFuncSetAttribute(attention_mixed_mma_kernel<HP_, UPW_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                               (int)smem) != cudaSuccess)                                                                  \
+        return leb_fail("leb_attention_mixed_mma: %zu bytes of shared memory per block refused", smem);                   \
+      set = smem;                                                                                                          \
+    }                                                                                                                      \
+    leb_launch(attention_mixed_mma_kernel<HP_, UPW_>, grid, block, smem, st, (bf16*)out, (const bf16*)q, ldq,              \
+               (const bf16*)k_pool, (const bf16*)v_pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen,  \
+               talk, gate, ldg, H, G, hd, vd, page_size, window, scale);                                                   \
+  }
+#define AMM_UPW(HP_)                            \
+  {                                             \
+    if (upw == 1) AMM_LAUNCH(HP_, 1)            \
+    else if (upw == 2) AMM_LAUNCH(HP_, 2)       \
+    else if (upw == 4) AMM_LAUNCH(HP_, 4)       \
+    else if (upw == 8) AMM_LAUNCH(HP_, 8)       \
+    else AMM_LAUNCH(HP_, 16)                    \
+  }
+  if (HP == 4) AMM_UPW(4)
+  else if (HP == 8) AMM_UPW(8)
+  else if (HP == 16) AMM_UPW(16)
+  else AMM_UPW(32)
+#undef AMM_UPW
+#undef AMM_LAUNCH
+  LEB_CHECK_LAUNCH("leb_attention_mixed_mma");
+  return 0;
+}
+
 // Bytes of shared memory a block needs for the given shape.
 static size_t amx_smem(int H, int G, int hd, int vd, int QT, int KT, size_t esz) {
   const int EV = (int)(16 / esz);

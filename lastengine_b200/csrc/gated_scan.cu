@@ -62,14 +62,121 @@ min_gru_kernel(TO* __restrict__ out, const float* __restrict__ pz, const float* 
   if (slot >= 0) state[(size_t)slot * W + c] = S;
 }
 
+// Long prompts: the rows of a sequence are cut into pieces of GRU_PIECE rows that run side by side.  The
+// recurrence S_t = a_t S_(t-1) + b_t (a = 1 - z, b = z c) of a piece, started from zero, gives the piece's two
+// numbers A = prod a_t and B = its last S; a piece's true start is the state carried in through the pieces before
+// it, S_in(p) = A(p-1) S_in(p-1) + B(p-1), a short walk that every thread of the second launch does for itself.
+constexpr int GRU_PIECE = 64;
+
+__global__ void __launch_bounds__(128)
+min_gru_pieces_kernel(float* __restrict__ sumA, float* __restrict__ sumB, const float* __restrict__ pz,
+                      const float* __restrict__ px, int ldp, const float* __restrict__ bz, const float* __restrict__ bx,
+                      const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen, int W, int max_pieces) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const int p = blockIdx.y, b = blockIdx.z;
+  const int n = seq_qlen[b];
+  const int t0 = p * GRU_PIECE;
+  if (t0 >= n) return;
+  const int rows = min(GRU_PIECE, n - t0);
+  const size_t m0 = (size_t)seq_qstart[b] + t0;
+  const float zb = bz ? bz[c] : 0.f, xb = bx ? bx[c] : 0.f;
+  float A = 1.f, S = 0.f;
+#pragma unroll 4
+  for (int t = 0; t < rows; t++) {
+    const float z = gs_sigmoid(pz[(m0 + t) * ldp + c] + zb);
+    const float u = px[(m0 + t) * ldp + c] + xb;
+    const float cand = u >= 0.f ? u + 0.5f : gs_sigmoid(u);
+    A *= 1.0f - z;
+    S = (1.0f - z) * S + z * cand;
+  }
+  sumA[((size_t)b * max_pieces + p) * W + c] = A;
+  sumB[((size_t)b * max_pieces + p) * W + c] = S;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+min_gru_finish_kernel(TO* __restrict__ out, const float* __restrict__ sumA, float* sumB,
+                      const float* __restrict__ pz, const float* __restrict__ px, const float* __restrict__ pg, int ldp,
+                      const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state,
+                      const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
+                      int W, int max_pieces) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const int p = blockIdx.y, b = blockIdx.z;
+  const int n = seq_qlen[b];
+  const int t0 = p * GRU_PIECE;
+  if (t0 >= n) return;
+  const int rows = min(GRU_PIECE, n - t0);
+  const int slot = seq_slot[b];
+  const size_t m0 = (size_t)seq_qstart[b] + t0;
+  const float zb = bz ? bz[c] : 0.f, xb = bx ? bx[c] : 0.f;
+  float S = slot >= 0 ? state[(size_t)slot * W + c] : 0.f;
+  for (int q = 0; q < p; q++) {
+    const size_t at = ((size_t)b * max_pieces + q) * W + c;
+    S = sumA[at] * S + sumB[at];
+  }
+#pragma unroll 4
+  for (int t = 0; t < rows; t++) {
+    const float z = gs_sigmoid(pz[(m0 + t) * ldp + c] + zb);
+    const float u = px[(m0 + t) * ldp + c] + xb;
+    const float g = pg[(m0 + t) * ldp + c];
+    const float cand = u >= 0.f ? u + 0.5f : gs_sigmoid(u);
+    S = (1.0f - z) * S + z * cand;
+    out[(m0 + t) * W + c] = from_f32<TO>(S * (g / (1.0f + expf(-g))));
+  }
+  // The piece that holds the sequence's last row leaves the state.  Every piece read the carried state above, and
+  // the write must not pass those reads: the pieces of a sequence are blocks of one launch that may run in any
+  // order, so the new state goes to the scratch row of this piece and a third, tiny launch stores it.
+  if (t0 + rows == n) sumB[((size_t)b * max_pieces + p) * W + c] = S;
+}
+
+__global__ void __launch_bounds__(128)
+min_gru_state_kernel(float* __restrict__ state, const float* __restrict__ sumB, const int* __restrict__ seq_slot,
+                     const int* __restrict__ seq_qlen, int W, int max_pieces) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  const int slot = seq_slot[b], n = seq_qlen[b];
+  if (c >= W || slot < 0 || n <= 0) return;
+  const int last = (n - 1) / GRU_PIECE;
+  state[(size_t)slot * W + c] = sumB[((size_t)b * max_pieces + last) * W + c];
+}
+
+LEB_API int leb_min_gru_piece_rows() { return GRU_PIECE; }
+
 // out [M, W] in the activation type; pz, px, pg float with one row stride (column ranges of one projection);
 // bz, bx [W] or null; state [slots][W]; seq_qlen null: one row per sequence.
+// scratch: null, or 2 * B * ceil(max_qlen / leb_min_gru_piece_rows()) * W floats: the rows of long sequences then
+// run in pieces side by side (three launches).
 LEB_API int leb_min_gru(void* out, int dtype, const float* pz, const float* px, const float* pg, int ldp, const float* bz,
                         const float* bx, float* state, const int* seq_slot, const int* seq_qstart, const int* seq_qlen,
-                        int B, int W, cudaStream_t st) {
+                        int B, int W, int max_qlen, float* scratch, cudaStream_t st) {
   if (B <= 0 || W <= 0) return 0;
   LEB_REQUIRE(B <= 65535, "leb_min_gru: step too large");
+  LEB_REQUIRE(dtype == LEB_F32 || dtype == LEB_BF16, "leb_min_gru: unknown dtype %d", dtype);
   LebPlainLaunches plain(true);
+  if (scratch && seq_qlen && max_qlen > GRU_PIECE) {
+    const int pieces = ceil_div(max_qlen, GRU_PIECE);
+    LEB_REQUIRE(pieces <= 65535, "leb_min_gru: step too large");
+    float* sumA = scratch;
+    float* sumB = scratch + (size_t)B * pieces * W;
+    const dim3 grid(ceil_div(W, 128), pieces, B), block(128);
+    leb_launch(min_gru_pieces_kernel, grid, block, 0, st, sumA, sumB, pz, px, ldp, bz, bx, seq_qstart, seq_qlen, W, pieces);
+    LEB_CHECK_LAUNCH("leb_min_gru (pieces)");
+    if (dtype == LEB_F32)
+      leb_launch(min_gru_finish_kernel<float>, grid, block, 0, st, (float*)out, sumA, sumB, pz, px, pg, ldp, bz, bx, state,
+                 seq_slot, seq_qstart, seq_qlen, W, pieces);
+    else
+      leb_launch(min_gru_finish_kernel<bf16>, grid, block, 0, st, (bf16*)out, sumA, sumB, pz, px, pg, ldp, bz, bx, state,
+                 seq_slot, seq_qstart, seq_qlen, W, pieces);
+    LEB_CHECK_LAUNCH("leb_min_gru (finish)");
+    leb_launch(min_gru_state_kernel, dim3(ceil_div(W, 128), B), block, 0, st, state, sumB, seq_slot, seq_qlen, W, pieces);
+    LEB_CHECK_LAUNCH("leb_min_gru (state)");
+    return 0;
+  }
   const dim3 grid(ceil_div(W, 128), B), block(128);
   if (dtype == LEB_F32)
     leb_launch(min_gru_kernel<float>, grid, block, 0, st, (float*)out, pz, px, pg, ldp, bz, bx, state, seq_slot, seq_qstart,
@@ -83,44 +190,57 @@ LEB_API int leb_min_gru(void* out, int dtype, const float* pz, const float* px, 
   return 0;
 }
 
-// A block takes a sequence.  decay and write hold f and i between the phases; mrow gets m_t of every row.
+// A block takes a sequence and walks its rows in pieces that fit shared memory: the gates of a piece's rows are
+// formed side by side into shared memory, the maximum walks the piece there (one thread a head, nothing but
+// an addition and a maximum per row, no trip to global memory inside the walk), and the exponentials are
+// again formed side by side.
+constexpr int EXG_FLOATS = 3 * 4096;      // shared floats of a block: f, i and m of a piece
 __global__ void __launch_bounds__(256)
 exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __restrict__ mrow, const float* __restrict__ pi,
                  const float* __restrict__ pf, int ldp, const float* __restrict__ bi, const float* __restrict__ bf, float cap,
                  float* __restrict__ mstate, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
-                 const int* __restrict__ seq_qlen, int H) {
+                 const int* __restrict__ seq_qlen, int H, int piece) {
+  __shared__ float sm[EXG_FLOATS];
   pdl_wait();
   const int b = blockIdx.x;
   const int slot = seq_slot[b];
   const int n = seq_qlen ? seq_qlen[b] : 1;
   const size_t m0 = seq_qstart[b];
-  for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
-    const int t = idx / H, h = idx - t * H;
-    const float ri = pi[(m0 + t) * ldp + h] + (bi ? bi[h] : 0.f);
-    const float rf = pf[(m0 + t) * ldp + h] + (bf ? bf[h] : 0.f);
-    write[(m0 + t) * H + h] = cap * tanhf(ri / cap);
-    decay[(m0 + t) * H + h] = gs_log_sigmoid(cap * tanhf(rf / cap));
-  }
-  __syncthreads();
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    float m = slot >= 0 ? mstate[(size_t)slot * H + h] : 0.f;
-    for (int t = 0; t < n; t++) {
-      m = fmaxf(decay[(m0 + t) * H + h] + m, write[(m0 + t) * H + h]);
-      mrow[(m0 + t) * H + h] = m;
+  float* fs = sm;                       // [piece][H]
+  float* is = sm + (size_t)piece * H;
+  float* ms = is + (size_t)piece * H;   // [piece + 1][H]: row 0 holds the maximum before the piece
+  for (int h = threadIdx.x; h < H; h += blockDim.x) ms[h] = slot >= 0 ? mstate[(size_t)slot * H + h] : 0.f;
+  for (int t0 = 0; t0 < n; t0 += piece) {
+    const int rows = min(piece, n - t0);
+    for (int idx = threadIdx.x; idx < rows * H; idx += blockDim.x) {
+      const int t = idx / H, h = idx - t * H;
+      const float ri = pi[(m0 + t0 + t) * ldp + h] + (bi ? bi[h] : 0.f);
+      const float rf = pf[(m0 + t0 + t) * ldp + h] + (bf ? bf[h] : 0.f);
+      is[idx] = cap * tanhf(ri / cap);
+      fs[idx] = gs_log_sigmoid(cap * tanhf(rf / cap));
     }
+    __syncthreads();
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      float m = ms[h];
+      for (int t = 0; t < rows; t++) {
+        m = fmaxf(fs[t * H + h] + m, is[t * H + h]);
+        ms[(t + 1) * H + h] = m;
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * H; idx += blockDim.x) {
+      const float before = ms[idx], now = ms[idx + H];
+      const size_t at = (m0 + t0) * H + idx;
+      decay[at] = expf(fs[idx] + before - now);
+      write[at] = expf(is[idx] - now);
+      mrow[at] = now;
+    }
+    __syncthreads();
+    for (int h = threadIdx.x; h < H; h += blockDim.x) ms[h] = ms[rows * H + h];      // each thread its own heads: no race
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
-    const int t = idx / H, h = idx - t * H;
-    const float before = t > 0 ? mrow[(m0 + t - 1) * H + h] : (slot >= 0 ? mstate[(size_t)slot * H + h] : 0.f);
-    const float now = mrow[(m0 + t) * H + h];
-    const float f = decay[(m0 + t) * H + h], i = write[(m0 + t) * H + h];
-    decay[(m0 + t) * H + h] = expf(f + before - now);
-    write[(m0 + t) * H + h] = expf(i - now);
-  }
-  __syncthreads();      // every read of the carried maximum is done
   if (slot >= 0 && n > 0)
-    for (int h = threadIdx.x; h < H; h += blockDim.x) mstate[(size_t)slot * H + h] = mrow[(m0 + n - 1) * H + h];
+    for (int h = threadIdx.x; h < H; h += blockDim.x) mstate[(size_t)slot * H + h] = ms[h];
 }
 
 // decay, write, mrow [M, H] float; pi, pf float with one row stride; bi, bf [H] or null; mstate [slots][H].
@@ -129,9 +249,11 @@ LEB_API int leb_exp_gates(float* decay, float* write, float* mrow, const float* 
                           const int* seq_qlen, int B, int H, cudaStream_t st) {
   if (B <= 0 || H <= 0) return 0;
   LEB_REQUIRE(cap > 0.f, "leb_exp_gates: the gates' cap must be positive, got %g", (double)cap);
+  LEB_REQUIRE(H <= 2048, "leb_exp_gates: %d heads (up to 2048)", H);
   LebPlainLaunches plain(true);
+  const int piece = min(256, (EXG_FLOATS / 3 - H) / H);      // rows of a piece: f, i and m (one row more) fit
   leb_launch(exp_gates_kernel, dim3(B), dim3(256), 0, st, decay, write, mrow, pi, pf, ldp, bi, bf, cap, mstate, seq_slot,
-             seq_qstart, seq_qlen, H);
+             seq_qstart, seq_qlen, H, piece);
   LEB_CHECK_LAUNCH("leb_exp_gates");
   return 0;
 }

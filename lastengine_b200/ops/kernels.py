@@ -153,13 +153,15 @@ def _declare(L) -> None:
         "leb_gemm_bf16_tc_slices": [I, I, I],
         "leb_gemm_bf16_tc_sliced": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
         "leb_gated_recurrence": [P, I, P, P, I, P, I, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
-        "leb_min_gru": [P, I, P, P, P, I, P, P, P, P, P, P, I, I, P],
+        "leb_min_gru": [P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, P, P],
         "leb_exp_gates": [P, P, P, P, P, I, P, P, F, P, P, P, P, I, I, P],
         "leb_exp_gates_finish": [P, I, P, P, P, I, P, F, F, I, I, I, P],
         "leb_layernorm_pair": [P, P, I, P, P, F, P, P, I, I, F, P],
         "leb_activation": [P, I, P, I, I, I, I, P],
         "leb_weighted_pair_sum": [P, P, P, F, P, F, I, I, I, P],
         "leb_attention_mixed": [P, P, P, I, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
+        "leb_attention_mixed_mma": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
+        "leb_attention_mixed_mma_supported": [I, I, I, I, I],
         "leb_delta_prep": [P, P, P, P, P, P, I, P, I, P, I, P, P, I, I, I, I, I, F, F, P],
         "leb_ssm_prep": [P, I, I, P, P, P, P, I, P, P, I, I, P],
         "leb_group_norm_gate": [P, I, P, P, I, P, I, I, I, I, F, I, P],
@@ -454,10 +456,11 @@ def group_norm_gate(out: torch.Tensor, y: torch.Tensor, z: torch.Tensor, w: torc
 
 
 def min_gru(out: torch.Tensor, pz: torch.Tensor, px: torch.Tensor, pg: torch.Tensor, bz: torch.Tensor | None,
-            bx: torch.Tensor | None, state: torch.Tensor, batch) -> None:
+            bx: torch.Tensor | None, state: torch.Tensor, batch, scratch: torch.Tensor | None = None) -> None:
     """The minimal gated recurrent unit over the step's rows, per channel and sequence (all float):
     z = sigmoid(pz + bz), u = px + bx, c = u + 1/2 where u >= 0 else sigmoid(u), S <- (1 - z) S + z c,
-    out = S * silu(pg) in out's type.  pz, px, pg float [M, W] with one row stride; state [slots, W]."""
+    out = S * silu(pg) in out's type.  pz, px, pg float [M, W] with one row stride; state [slots, W].  `scratch`
+    (float, `min_gru_scratch` numbers): sequences that bring many rows then run in pieces side by side."""
     _cuda(out, "min_gru.out")
     M, W = out.shape
     ldp = _f32_rows(pz, "min_gru.pz", M, W)
@@ -469,9 +472,28 @@ def min_gru(out: torch.Tensor, pz: torch.Tensor, px: torch.Tensor, pg: torch.Ten
     _cuda(state, "min_gru.state", torch.float32)
     assert state.shape[1:] == (W,)
     single = batch.max_qlen == 1 and M == batch.n_seqs
+    if scratch is not None:
+        _cuda(scratch, "min_gru.scratch", torch.float32)
+        if scratch.numel() < min_gru_scratch(batch, W):
+            raise KernelError(f"min_gru: scratch of {scratch.numel()} numbers, {min_gru_scratch(batch, W)} needed")
     _check(lib().leb_min_gru(_ptr(out), _dt(out, "min_gru.out"), _ptr(pz), _ptr(px), _ptr(pg), ldp, _ptr(bz), _ptr(bx),
                              _ptr(state), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
-                             None if single else _ptr(batch.seq_qlen), batch.n_seqs, W, _stream()))
+                             None if single else _ptr(batch.seq_qlen), batch.n_seqs, W, batch.max_qlen, _ptr(scratch),
+                             _stream()))
+
+
+_gru_piece = [0]
+
+
+def min_gru_scratch(batch, W: int) -> int:
+    """Floats of scratch with which `min_gru` runs a step's long sequences in pieces (0: the step has none)."""
+    if not _gru_piece[0]:
+        fn = lib().leb_min_gru_piece_rows
+        fn.restype, fn.argtypes = c_int, []
+        _gru_piece[0] = int(fn())
+    if batch.max_qlen <= _gru_piece[0]:
+        return 0
+    return 2 * batch.n_seqs * (-(-batch.max_qlen // _gru_piece[0])) * W
 
 
 def exp_gates(decay: torch.Tensor, write: torch.Tensor, mrow: torch.Tensor, pi: torch.Tensor, pf: torch.Tensor,
@@ -577,6 +599,15 @@ def mixed_attention_splits(batch, H: int, window: int) -> int:
     return max(1, min(keys // 128, -(-sm_count() // max(1, batch.n_seqs)), 32))
 
 
+MIXED_MMA_MIN_ROWS = 8      # longest row count of a sequence from which bfloat16 prompts go to the tensor-core kernel
+_MIXED_MMA = [True]
+
+
+def set_mixed_attention_mma(on: bool) -> None:
+    """Tests switch the tensor-core kernel of the mixed-heads attention off to compare it with the general one."""
+    _MIXED_MMA[0] = bool(on)
+
+
 def attention_mixed(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                     batch, talk: torch.Tensor, gate: torch.Tensor | None, nh: int, nkv: int, hd: int, vd: int,
                     page_size: int, window: int, scale: float, n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
@@ -599,6 +630,15 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_
         if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"attention_mixed: {n_splits} splits need {need} floats of scratch")
     single = batch.max_qlen == 1 and M == batch.n_seqs
+    L = lib()
+    if (_MIXED_MMA[0] and out.dtype == torch.bfloat16 and n_splits == 1 and batch.max_qlen >= MIXED_MMA_MIN_ROWS
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and L.leb_attention_mixed_mma_supported(nh, nkv, hd, vd, page_size)):
+        _check(L.leb_attention_mixed_mma(
+            _ptr(out), _ptr(q), q.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+            _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(talk), _ptr(gate),
+            ldg, M, batch.n_seqs, nh, nkv, hd, vd, page_size, int(window), float(scale), batch.max_qlen, _stream()))
+        return
     _check(lib().leb_attention_mixed(
         _ptr(out), _ptr(scratch), _ptr(q), q.stride(0), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention_mixed"),
         _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart),

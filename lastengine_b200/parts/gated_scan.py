@@ -63,7 +63,10 @@ class MinGRUMixer(Mixer):
         proj = ws.get("gru.proj", (M, 3 * W), torch.float32)
         kernels.linear(proj, h, self.w_in)
         s = ws.get("gru.s", (M, W), env.dtype)
-        kernels.min_gru(s, proj[:, :W], proj[:, W: 2 * W], proj[:, 2 * W:], self.bz, self.bx, cache.state, batch)
+        n = kernels.min_gru_scratch(batch, W)
+        scratch = ws.get("gru.pieces", (n,), torch.float32) if n else None
+        kernels.min_gru(s, proj[:, :W], proj[:, W: 2 * W], proj[:, 2 * W:], self.bz, self.bx, cache.state, batch,
+                        scratch=scratch)
         kernels.linear(out, s, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE)
 
 

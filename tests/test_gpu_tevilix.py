@@ -60,6 +60,39 @@ def test_attention_alone_whole_in_portions_and_batched(heads, kv, dim, vdim, sca
                                [0, 2, 3, 8, 9, 21], TOL[dtype], dtype == "bfloat16")
 
 
+MMA_CASES = [  # heads, kv heads, dim, vdim, window: sizes the tensor-core kernel takes
+    (4, 2, 128, 128, 72), (6, 2, 32, 16, 20), (32, 8, 64, 64, 200), (16, 4, 64, 32, 0), (3, 3, 64, 64, 70), (8, 1, 16, 8, 33),
+    (32, 2, 16, 64, 100), (2, 2, 256, 24, 150),
+]
+
+
+@pytest.mark.parametrize("heads,kv,dim,vdim,size", MMA_CASES)
+def test_tensor_core_attention_against_the_general_kernel_and_the_plain_one(heads, kv, dim, vdim, size):
+    """bfloat16 prompts of 8 rows and more run the tensor-core kernel: whole, in portions that start and end off the
+    tile grid, batched with unequal lengths; the same steps through the general kernel give the same numbers up to the
+    rounding of the two kernels' different orders of summation."""
+    assert K().lib().leb_attention_mixed_mma_supported(heads, kv, dim, vdim, 64)
+    D = 48
+    m = att(heads, kv, dim, vdim, 0.2, 16, 10000.0, 2.0, size)
+    outs = {}
+    for mma in (True, False):
+        K().set_mixed_attention_mma(mma)
+        try:
+            rig = MixerRig("mixed_heads_attention", att_params(D, heads, kv, dim, vdim, 0.2, 16, 10000.0, 2.0, size), "bfloat16", seed=3)
+            hs = [inputs(n, D, 70 + n, True) for n in (300, 9, 77)]
+            slots = [rig.cache.alloc_seq() for _ in hs]
+            got = [rig.step(slots, [h[:n] for h, n in zip(hs, (131, 8, 40))]), rig.step(slots, [h[n:] for h, n in zip(hs, (131, 8, 40))])]
+            outs[mma] = [np.concatenate([a, b]) for a, b in zip(*got)]
+            for s_ in slots:
+                rig.cache.free_seq(s_)
+        finally:
+            K().set_mixed_attention_mma(True)
+    for h, a, b in zip(hs, outs[True], outs[False]):
+        want = P.mixed_heads_attention(h, rig.plain, m, 1e-5)
+        assert err(a, want) < H.TOL_BF16 and err(b, want) < H.TOL_BF16
+        assert err(a, b) < H.TOL_BF16 / 2
+
+
 def test_the_mixing_matrix_matters_and_is_applied_before_the_softmax():
     """With the identity in its place the result is plain attention and far from the mixed one; a matrix that
     copies head 1's scores into head 0 makes head 0 weigh its own values by head 1's weights."""

@@ -55,7 +55,7 @@ T_A = {
 
 # heads of 64 and 128, a window longer than a page, every layer looped, one choice of many, groups of one expert
 T_B = {
-    "architecture": "Tevilix", "vocab": 150, "width": 72, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+    "architecture": "Tevilix", "vocab": 150, "width": 72, "norm": {"eps": 1e-6}, "embedding": {"scale": 6.0},
     "layers": [
         layer("parallel", par(att(3, 3, 64, 64, 0.125, 64, 200000.0, 1.0, 70), 1.2, 40, 0.5), moe(12, 1, 3, 1, 2.0, 16)),
         layer("mlstm", mls(3, 32, 64, 10.0), moe(4, 2, 4, 3, 0.5, 40)),
