@@ -597,7 +597,7 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             if label == "tevilix":
                 wp, wd = _tevilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS), _tevilix_kernel_work(cfg, 8, 8, 2048)
                 by = {"prefill": wp["bytes"], "decode_b8": wd["bytes"]}
-                fl = {"prefill": wp["flops"]}
+                fl = {"prefill": dict(wp["flops"], leb_attention_mixed_mma=wp["flops"]["leb_attention_mixed"])}
             elif label == "kisilix":
                 wp, wd = _kisilix_kernel_work(cfg, PREFILL_TOKENS, 1, PREFILL_TOKENS), _kisilix_kernel_work(cfg, 8, 8, 2048)
                 by = {"prefill": wp["bytes"], "decode_b8": wd["bytes"]}

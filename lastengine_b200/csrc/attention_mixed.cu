@@ -350,17 +350,19 @@ attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part
 //   1. the tile's keys of every kv head go to shared memory; every warp forms raw score tiles S_g = Q_g K^T
 //      (16 rows x 8 keys, mma.sync m16n8k16, bfloat16 operands, float sums) for its share of the (head, 8 keys)
 //      pairs and leaves them, times the scale, in shared memory as floats;
-//   2. warp i takes row i with a lane per key: it reads the row's raw scores of all heads once, mixes them into
-//      every head's score with the [heads, heads] matrix (float multiply-adds, the matrix transposed in shared
-//      memory so that four heads' factors are one load), masks, and runs the streaming softmax of every head
-//      (lane h keeps head h's running maximum and sum); the weights go back over the row's raw scores as two
-//      bfloat16 terms, hi = bf16(p) and lo = bf16(p - hi), so that the product with the values sees 16
-//      significant bits of p; meanwhile the tile's values arrive in the buffer the keys have left;
+//   2. warp i takes row i, first with a lane per key: it reads the row's raw scores of all heads once, mixes them
+//      into every head's score with the [heads, heads] matrix (float multiply-adds, the matrix transposed in
+//      shared memory so that four heads' factors are one load), masks, and puts the mixed scores back over the raw
+//      ones; then with a lane per head: lane h reads head h's 32 scores of the row (16 bytes a load), and runs the
+//      streaming softmax on them in its own registers (no exchange between lanes; lane h keeps head h's running
+//      maximum and sum); the weights go back over the scores as two bfloat16 terms, hi = bf16(p) and
+//      lo = bf16(p - hi), so that the product with the values sees 16 significant bits of p; meanwhile the
+//      tile's values arrive in the buffer the keys have left;
 //   3. every warp adds P V for its share of the (head, 8 value dimensions) pairs (two products, hi and lo),
 //      after scaling its sums by the factor the softmax left for (head, row).
 // Float everywhere outside the products' operands.  Sizes: up to 32 heads, key heads in multiples of 16 numbers,
 // value heads in multiples of 8, heads x value size up to 2,048 (a thread then holds 64 sums).
-constexpr int AMM_ROWS = 16, AMM_KT = 32, AMM_WARPS = 16, AMM_SLOT = 36;
+constexpr int AMM_ROWS = 16, AMM_KT = 32, AMM_WARPS = 16, AMM_SLOT = 36, AMM_ROW_PAD = 4;
 
 __device__ __forceinline__ void amm_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -368,9 +370,38 @@ __device__ __forceinline__ void amm_mma(float* d, const uint32_t* a, uint32_t b0
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Shared memory: talkT [H][HP] floats | corr [H][16] floats | raw / P [H][16][AMM_SLOT] floats (a row's 32 raw
-// scores, later its weights: hi in the first 16 words, lo in the next 16) | q [H][16][hd + 8] bfloat16 |
-// keys [G][32][hd + 8] or values [G][vd][40] bfloat16 (one buffer).
+// Four 8 x 8 tiles of 16-bit numbers from shared memory, a row (16 bytes) per lane's address: the A operand of a product.
+__device__ __forceinline__ void amm_ldsm4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+// Two tiles: the B operand (lanes 0..15 give the addresses).
+__device__ __forceinline__ void amm_ldsm2(uint32_t& r0, uint32_t& r1, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r0), "=r"(r1) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+// Two float multiply-adds in one instruction (sm_100): acc = a * b + acc on both halves of the 64-bit registers.
+__device__ __forceinline__ void amm_fma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long amm_pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void amm_unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ float amm_exp2(float x) {      // 2^x from the special function unit (relative error about 2^-22)
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Shared memory: talkT [H][HP] floats | corr [H][16] floats | raw / P [16][H][AMM_SLOT] (+ AMM_ROW_PAD a row) floats
+// (a (row, head)'s 32 raw scores, then its mixed scores, then its weights: hi in the first 16 words, lo in the
+// next 16; the strides keep the products' fragment loads, a lane per key and a lane per head all off each other's
+// banks) | q [H][16][hd + 8] bfloat16 | keys [G][32][hd + 8] or values [G][vd][40] bfloat16 (one buffer).
 template <int HP, int UPW>
 __global__ void __launch_bounds__(32 * AMM_WARPS, 1)
 attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ k_pool,
@@ -398,7 +429,8 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
   float* talkT = reinterpret_cast<float*>(amm_sm);            // [g][HP]
   float* corr_s = talkT + H * HP;                             // [h][16]
   float* raw_s = corr_s + H * AMM_ROWS;                       // [h][16][AMM_SLOT]
-  bf16* q_s = reinterpret_cast<bf16*>(raw_s + (size_t)H * AMM_ROWS * AMM_SLOT);   // [g][16][QS]
+  const int RS = H * AMM_SLOT + AMM_ROW_PAD;                  // words of a row of raw_s
+  bf16* q_s = reinterpret_cast<bf16*>(raw_s + (size_t)AMM_ROWS * RS);   // [g][16][QS]
   bf16* kv_s = q_s + (size_t)H * AMM_ROWS * QS;
 
   if (slot < 0) {      // a padding sequence: a defined result, no cache access
@@ -430,7 +462,8 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
   for (int u = 0; u < UPW; u++)
 #pragma unroll
     for (int x = 0; x < 4; x++) acc[u][x] = 0.f;
-  float m_run = AMX_NEG, l_run = 0.f;      // of head `lane` and row `warp`
+  float m_run = AMX_NEG, l_run = 0.f;      // of head `lane` and row `warp`, kept by that lane alone
+  const float scale2 = scale * 1.4426950408889634f;
 
   for (int ut = 0; ut < n_tiles; ut++) {
     const int key0 = (tile_first + ut) * AMM_KT;
@@ -449,28 +482,31 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
       }
     }
     __syncthreads();
-    // 1. raw scores: units (head g, 8 keys nt)
-    for (int u = warp; u < H * (AMM_KT / 8); u += AMM_WARPS) {
-      const int g = u / (AMM_KT / 8), nt = u - g * (AMM_KT / 8);
-      const bf16* qa = q_s + (size_t)g * AMM_ROWS * QS;
-      const bf16* kb = kv_s + ((size_t)(g / Gq) * AMM_KT + nt * 8 + gid) * KS;
-      float d[4] = {0.f, 0.f, 0.f, 0.f};
+    // 1. raw scores, a head a unit: the head's query fragments stay in registers over the tile's four groups of 8 keys.
+    //    The scale carries log2(e), so the softmax below works with powers of two.
+    for (int g = warp; g < H; g += AMM_WARPS) {
+      const bf16* qa = q_s + (size_t)g * AMM_ROWS * QS + (size_t)(lane & 15) * QS + 8 * (lane >> 4);
+      const bf16* kb = kv_s + ((size_t)(g / Gq) * AMM_KT + (lane & 7)) * KS + 8 * ((lane >> 3) & 1);
+      float d[AMM_KT / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < AMM_KT / 8; nt++) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
       for (int k0 = 0; k0 < hd; k0 += 16) {
         uint32_t a[4];
-        a[0] = *reinterpret_cast<const uint32_t*>(qa + (size_t)gid * QS + k0 + 2 * tig);
-        a[1] = *reinterpret_cast<const uint32_t*>(qa + (size_t)(gid + 8) * QS + k0 + 2 * tig);
-        a[2] = *reinterpret_cast<const uint32_t*>(qa + (size_t)gid * QS + k0 + 8 + 2 * tig);
-        a[3] = *reinterpret_cast<const uint32_t*>(qa + (size_t)(gid + 8) * QS + k0 + 8 + 2 * tig);
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + k0 + 2 * tig);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + k0 + 8 + 2 * tig);
-        amm_mma(d, a, b0, b1);
+        amm_ldsm4(a, qa + k0);
+#pragma unroll
+        for (int nt = 0; nt < AMM_KT / 8; nt++) {
+          uint32_t b0, b1;
+          amm_ldsm2(b0, b1, kb + (size_t)nt * 8 * KS + k0);
+          amm_mma(d[nt], a, b0, b1);
+        }
       }
-      float* r0 = raw_s + ((size_t)g * AMM_ROWS + gid) * AMM_SLOT + nt * 8 + 2 * tig;
-      float* r1 = raw_s + ((size_t)g * AMM_ROWS + gid + 8) * AMM_SLOT + nt * 8 + 2 * tig;
-      r0[0] = d[0] * scale;
-      r0[1] = d[1] * scale;
-      r1[0] = d[2] * scale;
-      r1[1] = d[3] * scale;
+#pragma unroll
+      for (int nt = 0; nt < AMM_KT / 8; nt++) {
+        float* r0 = raw_s + (size_t)gid * RS + g * AMM_SLOT + nt * 8 + 2 * tig;
+        float* r1 = raw_s + (size_t)(gid + 8) * RS + g * AMM_SLOT + nt * 8 + 2 * tig;
+        *reinterpret_cast<float2*>(r0) = make_float2(d[nt][0] * scale2, d[nt][1] * scale2);
+        *reinterpret_cast<float2*>(r1) = make_float2(d[nt][2] * scale2, d[nt][3] * scale2);
+      }
     }
     __syncthreads();      // the scores are complete; the keys are used up
     // the tile's values on their way: asked for now, stored after the softmax
@@ -491,42 +527,64 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
       const int i = warp;
       const int pos = pos_lo + i, key = key0 + lane;
       const bool seen = i < nrows && key <= pos && (window <= 0 || pos - key < window);
-      float t[HP];
+      unsigned long long t2[HP / 2];      // two heads' sums a register pair
 #pragma unroll
-      for (int h = 0; h < HP; h++) t[h] = 0.f;
+      for (int h = 0; h < HP / 2; h++) t2[h] = 0ull;
+      float* row = raw_s + (size_t)i * RS;
       for (int g = 0; g < H; g++) {
-        const float r = raw_s[((size_t)g * AMM_ROWS + i) * AMM_SLOT + lane];
-        const float4* tk = reinterpret_cast<const float4*>(talkT + g * HP);
+        const float r = row[g * AMM_SLOT + lane];
+        const unsigned long long rr = amm_pack2(r, r);
+        const ulonglong2* tk = reinterpret_cast<const ulonglong2*>(talkT + g * HP);
 #pragma unroll
         for (int h4 = 0; h4 < HP / 4; h4++) {
-          const float4 w4 = tk[h4];
-          t[4 * h4 + 0] = fmaf(w4.x, r, t[4 * h4 + 0]);
-          t[4 * h4 + 1] = fmaf(w4.y, r, t[4 * h4 + 1]);
-          t[4 * h4 + 2] = fmaf(w4.z, r, t[4 * h4 + 2]);
-          t[4 * h4 + 3] = fmaf(w4.w, r, t[4 * h4 + 3]);
+          const ulonglong2 w4 = tk[h4];
+          amm_fma2(t2[2 * h4], w4.x, rr);
+          amm_fma2(t2[2 * h4 + 1], w4.y, rr);
         }
       }
-      __syncwarp();      // every lane has read the row's raw scores before the weights overwrite them
+      float t[HP];
 #pragma unroll
-      for (int h = 0; h < HP; h++) {
-        if (h >= H) break;
-        const float tmax = warp_max(seen ? t[h] : AMX_NEG);
-        const float m_old = __shfl_sync(0xffffffffu, m_run, h);
-        const float l_old = __shfl_sync(0xffffffffu, l_run, h);
-        const float m_new = fmaxf(m_old, tmax);
-        const float w = seen ? expf(t[h] - m_new) : 0.f;
-        const float corr = expf(m_old - m_new);
-        const float l_new = l_old * corr + warp_sum(w);
-        if (lane == h) {
-          m_run = m_new;
-          l_run = l_new;
-          corr_s[h * AMM_ROWS + i] = corr;
+      for (int h = 0; h < HP / 2; h++) amm_unpack2(t2[h], t[2 * h], t[2 * h + 1]);
+      __syncwarp();      // every lane has read the row's raw scores before the mixed ones overwrite them
+#pragma unroll
+      for (int h = 0; h < HP; h++)
+        if (h < H) row[h * AMM_SLOT + lane] = seen ? t[h] : AMX_NEG;
+      __syncwarp();
+      if (lane < H) {      // head `lane`: its 32 scores of the row, the streaming softmax in registers
+        float4* mine = reinterpret_cast<float4*>(row + lane * AMM_SLOT);
+        float v[AMM_KT];
+#pragma unroll
+        for (int x = 0; x < AMM_KT / 4; x++) {
+          const float4 f = mine[x];
+          v[4 * x] = f.x; v[4 * x + 1] = f.y; v[4 * x + 2] = f.z; v[4 * x + 3] = f.w;
         }
-        const bf16 hi = __float2bfloat16_rn(w);
-        const bf16 lo = __float2bfloat16_rn(w - __bfloat162float(hi));
-        bf16* ps = reinterpret_cast<bf16*>(raw_s + ((size_t)h * AMM_ROWS + i) * AMM_SLOT);
-        ps[lane] = hi;
-        ps[32 + lane] = lo;
+        float tmax = v[0];
+#pragma unroll
+        for (int x = 1; x < AMM_KT; x++) tmax = fmaxf(tmax, v[x]);
+        const float m_new = fmaxf(m_run, tmax);
+        const float corr = amm_exp2(m_run - m_new);      // 1 while nothing was seen (both at the floor)
+        const float m_use = m_new > 0.5f * AMX_NEG ? m_new : 0.f;      // nothing seen yet: every weight is 2^(floor) = 0
+        float sum = 0.f;
+        uint32_t hi[AMM_KT / 2], lo[AMM_KT / 2];
+#pragma unroll
+        for (int x = 0; x < AMM_KT; x += 2) {
+          const float w0 = amm_exp2(v[x] - m_use);
+          const float w1 = amm_exp2(v[x + 1] - m_use);
+          sum += w0 + w1;
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(w0, w1);
+          const __nv_bfloat162 l2 = __floats2bfloat162_rn(w0 - __low2float(h2), w1 - __high2float(h2));
+          hi[x / 2] = *reinterpret_cast<const uint32_t*>(&h2);
+          lo[x / 2] = *reinterpret_cast<const uint32_t*>(&l2);
+        }
+        l_run = l_run * corr + sum;
+        m_run = m_new;
+        corr_s[lane * AMM_ROWS + i] = corr;
+        uint4* dst = reinterpret_cast<uint4*>(mine);
+#pragma unroll
+        for (int x = 0; x < AMM_KT / 8; x++) {
+          dst[x] = make_uint4(hi[4 * x], hi[4 * x + 1], hi[4 * x + 2], hi[4 * x + 3]);
+          dst[AMM_KT / 8 + x] = make_uint4(lo[4 * x], lo[4 * x + 1], lo[4 * x + 2], lo[4 * x + 3]);
+        }
       }
     }
     // the values [c][d][j], zero where no position is yet
@@ -558,23 +616,16 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
       acc[uu][1] *= c0;
       acc[uu][2] *= c1;
       acc[uu][3] *= c1;
-      const uint32_t* p0 = reinterpret_cast<const uint32_t*>(raw_s + ((size_t)h * AMM_ROWS + gid) * AMM_SLOT);
-      const uint32_t* p1 = reinterpret_cast<const uint32_t*>(raw_s + ((size_t)h * AMM_ROWS + gid + 8) * AMM_SLOT);
-      const bf16* vb = kv_s + ((size_t)(h / Gq) * vd + dt * 8 + gid) * VS;
+      // a lane's rows of the weights: row (lane % 16), the 8 keys from 8 * (lane / 16) on; hi at bytes 0.., lo at 64..
+      const unsigned char* pa = reinterpret_cast<const unsigned char*>(raw_s + (size_t)(lane & 15) * RS + h * AMM_SLOT) + 16 * (lane >> 4);
+      const bf16* vb = kv_s + ((size_t)(h / Gq) * vd + dt * 8 + (lane & 7)) * VS + 8 * ((lane >> 3) & 1);
 #pragma unroll
       for (int k0 = 0; k0 < AMM_KT; k0 += 16) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vb + k0 + 2 * tig);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(vb + k0 + 8 + 2 * tig);
-        uint32_t a[4];
-        a[0] = p0[k0 / 2 + tig];
-        a[1] = p1[k0 / 2 + tig];
-        a[2] = p0[k0 / 2 + 4 + tig];
-        a[3] = p1[k0 / 2 + 4 + tig];
+        uint32_t b0, b1, a[4];
+        amm_ldsm2(b0, b1, vb + k0);
+        amm_ldsm4(a, pa + 2 * k0);
         amm_mma(acc[uu], a, b0, b1);
-        a[0] = p0[16 + k0 / 2 + tig];
-        a[1] = p1[16 + k0 / 2 + tig];
-        a[2] = p0[16 + k0 / 2 + 4 + tig];
-        a[3] = p1[16 + k0 / 2 + 4 + tig];
+        amm_ldsm4(a, pa + 64 + 2 * k0);
         amm_mma(acc[uu], a, b0, b1);
       }
     }
@@ -608,7 +659,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
 
 static size_t amm_smem(int H, int HP, int G, int hd, int vd) {
   const size_t kv = (size_t)G * (size_t)max(AMM_KT * (hd + 8), vd * (AMM_KT + 8));
-  return sizeof(float) * ((size_t)H * HP + (size_t)H * AMM_ROWS + (size_t)H * AMM_ROWS * AMM_SLOT) +
+  return sizeof(float) * ((size_t)H * HP + (size_t)H * AMM_ROWS + (size_t)AMM_ROWS * (H * AMM_SLOT + AMM_ROW_PAD)) +
          2 * ((size_t)H * AMM_ROWS * (hd + 8) + kv);
 }
 

@@ -190,14 +190,28 @@ LEB_API int leb_min_gru(void* out, int dtype, const float* pz, const float* px, 
   return 0;
 }
 
-// A block takes a sequence and walks its rows in pieces that fit shared memory: the gates of a piece's rows are
-// formed side by side into shared memory, the maximum walks the piece there (one thread a head, nothing but
-// an addition and a maximum per row, no trip to global memory inside the walk), and the exponentials are
-// again formed side by side.
+// The gates of all rows side by side (first launch): write <- i, decay <- f.
+__global__ void __launch_bounds__(256)
+exp_gates_rows_kernel(float* __restrict__ decay, float* __restrict__ write, const float* __restrict__ pi,
+                      const float* __restrict__ pf, int ldp, const float* __restrict__ bi, const float* __restrict__ bf,
+                      float cap, int H, size_t total) {
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t m = idx / H;
+  const int h = (int)(idx - m * H);
+  const float ri = pi[m * ldp + h] + (bi ? bi[h] : 0.f);
+  const float rf = pf[m * ldp + h] + (bf ? bf[h] : 0.f);
+  write[idx] = cap * tanhf(ri / cap);
+  decay[idx] = gs_log_sigmoid(cap * tanhf(rf / cap));
+}
+
+// Second launch: a block takes a sequence and walks its rows in pieces that fit shared memory: the piece's f and i
+// come in side by side, the maximum walks the piece there (one thread a head, an addition and a maximum per row,
+// no trip to global memory inside the walk), and the exponentials are again formed side by side.
 constexpr int EXG_FLOATS = 3 * 4096;      // shared floats of a block: f, i and m of a piece
 __global__ void __launch_bounds__(256)
-exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __restrict__ mrow, const float* __restrict__ pi,
-                 const float* __restrict__ pf, int ldp, const float* __restrict__ bi, const float* __restrict__ bf, float cap,
+exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __restrict__ mrow,
                  float* __restrict__ mstate, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                  const int* __restrict__ seq_qlen, int H, int piece) {
   __shared__ float sm[EXG_FLOATS];
@@ -213,15 +227,14 @@ exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __
   for (int t0 = 0; t0 < n; t0 += piece) {
     const int rows = min(piece, n - t0);
     for (int idx = threadIdx.x; idx < rows * H; idx += blockDim.x) {
-      const int t = idx / H, h = idx - t * H;
-      const float ri = pi[(m0 + t0 + t) * ldp + h] + (bi ? bi[h] : 0.f);
-      const float rf = pf[(m0 + t0 + t) * ldp + h] + (bf ? bf[h] : 0.f);
-      is[idx] = cap * tanhf(ri / cap);
-      fs[idx] = gs_log_sigmoid(cap * tanhf(rf / cap));
+      const size_t at = (m0 + t0) * H + idx;
+      fs[idx] = decay[at];
+      is[idx] = write[at];
     }
     __syncthreads();
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
       float m = ms[h];
+#pragma unroll 8
       for (int t = 0; t < rows; t++) {
         m = fmaxf(fs[t * H + h] + m, is[t * H + h]);
         ms[(t + 1) * H + h] = m;
@@ -246,14 +259,17 @@ exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __
 // decay, write, mrow [M, H] float; pi, pf float with one row stride; bi, bf [H] or null; mstate [slots][H].
 LEB_API int leb_exp_gates(float* decay, float* write, float* mrow, const float* pi, const float* pf, int ldp, const float* bi,
                           const float* bf, float cap, float* mstate, const int* seq_slot, const int* seq_qstart,
-                          const int* seq_qlen, int B, int H, cudaStream_t st) {
-  if (B <= 0 || H <= 0) return 0;
+                          const int* seq_qlen, int M, int B, int H, cudaStream_t st) {
+  if (B <= 0 || H <= 0 || M <= 0) return 0;
   LEB_REQUIRE(cap > 0.f, "leb_exp_gates: the gates' cap must be positive, got %g", (double)cap);
   LEB_REQUIRE(H <= 2048, "leb_exp_gates: %d heads (up to 2048)", H);
   LebPlainLaunches plain(true);
   const int piece = min(256, (EXG_FLOATS / 3 - H) / H);      // rows of a piece: f, i and m (one row more) fit
-  leb_launch(exp_gates_kernel, dim3(B), dim3(256), 0, st, decay, write, mrow, pi, pf, ldp, bi, bf, cap, mstate, seq_slot,
-             seq_qstart, seq_qlen, H, piece);
+  const size_t total = (size_t)M * H;
+  leb_launch(exp_gates_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, decay, write, pi, pf, ldp, bi, bf,
+             cap, H, total);
+  LEB_CHECK_LAUNCH("leb_exp_gates (rows)");
+  leb_launch(exp_gates_kernel, dim3(B), dim3(256), 0, st, decay, write, mrow, mstate, seq_slot, seq_qstart, seq_qlen, H, piece);
   LEB_CHECK_LAUNCH("leb_exp_gates");
   return 0;
 }

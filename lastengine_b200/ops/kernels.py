@@ -154,7 +154,7 @@ def _declare(L) -> None:
         "leb_gemm_bf16_tc_sliced": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
         "leb_gated_recurrence": [P, I, P, P, I, P, I, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
         "leb_min_gru": [P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, P, P],
-        "leb_exp_gates": [P, P, P, P, P, I, P, P, F, P, P, P, P, I, I, P],
+        "leb_exp_gates": [P, P, P, P, P, I, P, P, F, P, P, P, P, I, I, I, P],
         "leb_exp_gates_finish": [P, I, P, P, P, I, P, F, F, I, I, I, P],
         "leb_layernorm_pair": [P, P, I, P, P, F, P, P, I, I, F, P],
         "leb_activation": [P, I, P, I, I, I, I, P],
@@ -517,7 +517,7 @@ def exp_gates(decay: torch.Tensor, write: torch.Tensor, mrow: torch.Tensor, pi: 
     single = batch.max_qlen == 1 and M == batch.n_seqs
     _check(lib().leb_exp_gates(_ptr(decay), _ptr(write), _ptr(mrow), _ptr(pi), _ptr(pf), ldp, _ptr(bi), _ptr(bf), float(cap),
                                _ptr(mstate), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
-                               None if single else _ptr(batch.seq_qlen), batch.n_seqs, H, _stream()))
+                               None if single else _ptr(batch.seq_qlen), M, batch.n_seqs, H, _stream()))
 
 
 def exp_gates_finish(out: torch.Tensor, y: torch.Tensor, mrow: torch.Tensor, gate: torch.Tensor, w: torch.Tensor,
@@ -596,7 +596,7 @@ def mixed_attention_splits(batch, H: int, window: int) -> int:
     if batch.max_qlen > 1:
         return 1
     keys = batch.max_kvlen if window <= 0 else min(batch.max_kvlen, window)
-    return max(1, min(keys // 128, -(-sm_count() // max(1, batch.n_seqs)), 32))
+    return max(1, min(keys // 64, -(-2 * sm_count() // max(1, batch.n_seqs)), 32))
 
 
 MIXED_MMA_MIN_ROWS = 8      # longest row count of a sequence from which bfloat16 prompts go to the tensor-core kernel
