@@ -402,7 +402,7 @@ __device__ __forceinline__ float amm_exp2(float x) {      // 2^x from the specia
 // (a (row, head)'s 32 raw scores, then its mixed scores, then its weights: hi in the first 16 words, lo in the
 // next 16; the strides keep the products' fragment loads, a lane per key and a lane per head all off each other's
 // banks) | q [H][16][hd + 8] bfloat16 | keys [G][32][hd + 8] or values [G][vd][40] bfloat16 (one buffer).
-template <int HP, int UPW>
+template <int HP, int UPW, bool AHEAD>
 __global__ void __launch_bounds__(32 * AMM_WARPS, 1)
 attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ k_pool,
                            const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int bt_width,
@@ -462,6 +462,12 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
   for (int u = 0; u < UPW; u++)
 #pragma unroll
     for (int x = 0; x < 4; x++) acc[u][x] = 0.f;
+  // AHEAD: a thread holds up to four 16-byte pieces of the next tile's keys while this tile's values are multiplied
+  // (the launch asks for it where the sums leave the registers for it)
+  constexpr int KPT = AHEAD ? 4 : 1;
+  uint4 kreg[KPT];
+  const int k_per_row = hd / 8, k_total = G * AMM_KT * k_per_row;
+  const bool k_ahead = AHEAD;
   float m_run = AMX_NEG, l_run = 0.f;      // of head `lane` and row `warp`, kept by that lane alone
   const float scale2 = scale * 1.4426950408889634f;
 
@@ -470,15 +476,23 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
     const int page = block_table[(size_t)b * bt_width + key0 / page_size];
     const int in_page = key0 % page_size;
     __syncthreads();      // the buffer is free (the values of the tile before are used up); q and talkT are in place
-    {      // keys [c][j][hd]
-      const int per_row = hd / 8, total = G * AMM_KT * per_row;
-      for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        const int c = idx / (AMM_KT * per_row), rest = idx - c * (AMM_KT * per_row);
-        const int j = rest / per_row, d0 = (rest - j * per_row) * 8;
+    if (k_ahead && ut > 0) {      // the keys were asked for while the tile before multiplied its values
+#pragma unroll
+      for (int x = 0; x < KPT; x++) {
+        const int idx = threadIdx.x + x * blockDim.x;
+        if (idx < k_total) {
+          const int cj = idx / k_per_row, d0 = (idx - cj * k_per_row) * 8;
+          *reinterpret_cast<uint4*>(kv_s + (size_t)cj * KS + d0) = kreg[x];
+        }
+      }
+    } else {      // keys [c][j][hd]
+      for (int idx = threadIdx.x; idx < k_total; idx += blockDim.x) {
+        const int cj = idx / k_per_row, d0 = (idx - cj * k_per_row) * 8;
+        const int c = cj / AMM_KT, j = cj - c * AMM_KT;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (page >= 0 && key0 + j < kv_len)
           v = *reinterpret_cast<const uint4*>(k_pool + (((size_t)page * G + c) * page_size + in_page + j) * hd + d0);
-        *reinterpret_cast<uint4*>(kv_s + ((size_t)c * AMM_KT + j) * KS + d0) = v;
+        *reinterpret_cast<uint4*>(kv_s + (size_t)cj * KS + d0) = v;
       }
     }
     __syncthreads();
@@ -531,6 +545,7 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
 #pragma unroll
       for (int h = 0; h < HP / 2; h++) t2[h] = 0ull;
       float* row = raw_s + (size_t)i * RS;
+#pragma unroll 4
       for (int g = 0; g < H; g++) {
         const float r = row[g * AMM_SLOT + lane];
         const unsigned long long rr = amm_pack2(r, r);
@@ -605,6 +620,22 @@ attention_mixed_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, i
       }
     }
     __syncthreads();
+    if (k_ahead && ut + 1 < n_tiles) {      // the next tile's keys on their way
+      const int nkey0 = key0 + AMM_KT;
+      const int npage = block_table[(size_t)b * bt_width + nkey0 / page_size];
+      const int nin = nkey0 % page_size;
+#pragma unroll
+      for (int x = 0; x < KPT; x++) {
+        const int idx = threadIdx.x + x * blockDim.x;
+        kreg[x] = make_uint4(0, 0, 0, 0);
+        if (idx < k_total) {
+          const int cj = idx / k_per_row, d0 = (idx - cj * k_per_row) * 8;
+          const int c = cj / AMM_KT, j = cj - c * AMM_KT;
+          if (npage >= 0 && nkey0 + j < kv_len)
+            kreg[x] = *reinterpret_cast<const uint4*>(k_pool + (((size_t)npage * G + c) * page_size + nin + j) * hd + d0);
+        }
+      }
+    }
     // 3. weighted values: units (head h, 8 dimensions dt)
 #pragma unroll
     for (int uu = 0; uu < UPW; uu++) {
@@ -687,17 +718,19 @@ LEB_API int leb_attention_mixed_mma(void* out, const void* q, int ldq, const voi
   int upw = ceil_div(units, AMM_WARPS);
   upw = upw <= 1 ? 1 : upw <= 2 ? 2 : upw <= 4 ? 4 : upw <= 8 ? 8 : 16;
   const dim3 grid(ceil_div(max_qlen, AMM_ROWS), B), block(32 * AMM_WARPS);
+  const bool ahead = upw <= 8 && HP <= 16 && G * AMM_KT * (hd / 8) <= 4 * 32 * AMM_WARPS;
   LebPlainLaunches plain(true);
-#define AMM_LAUNCH(HP_, UPW_)                                                                                              \
+#define AMM_LAUNCH(HP_, UPW_) { if (ahead) AMM_LAUNCH2(HP_, UPW_, true) else AMM_LAUNCH2(HP_, UPW_, false) }
+#define AMM_LAUNCH2(HP_, UPW_, AH_)                                                                                        \
   {                                                                                                                        \
     static size_t set = 48 * 1024;                                                                                         \
     if (smem > set) {                                                                                                      \
-      if (cudaFuncSetAttribute(attention_mixed_mma_kernel<HP_, UPW_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+      if (cudaFuncSetAttribute(attention_mixed_mma_kernel<HP_, UPW_, AH_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                (int)smem) != cudaSuccess)                                                                  \
         return leb_fail("leb_attention_mixed_mma: %zu bytes of shared memory per block refused", smem);                   \
       set = smem;                                                                                                          \
     }                                                                                                                      \
-    leb_launch(attention_mixed_mma_kernel<HP_, UPW_>, grid, block, smem, st, (bf16*)out, (const bf16*)q, ldq,              \
+    leb_launch(attention_mixed_mma_kernel<HP_, UPW_, AH_>, grid, block, smem, st, (bf16*)out, (const bf16*)q, ldq,         \
                (const bf16*)k_pool, (const bf16*)v_pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen,  \
                talk, gate, ldg, H, G, hd, vd, page_size, window, scale);                                                   \
   }
@@ -715,6 +748,7 @@ LEB_API int leb_attention_mixed_mma(void* out, const void* q, int ldq, const voi
   else AMM_UPW(32)
 #undef AMM_UPW
 #undef AMM_LAUNCH
+#undef AMM_LAUNCH2
   LEB_CHECK_LAUNCH("leb_attention_mixed_mma");
   return 0;
 }
