@@ -66,7 +66,7 @@ min_gru_kernel(TO* __restrict__ out, const float* __restrict__ pz, const float* 
 // recurrence S_t = a_t S_(t-1) + b_t (a = 1 - z, b = z c) of a piece, started from zero, gives the piece's two
 // numbers A = prod a_t and B = its last S; a piece's true start is the state carried in through the pieces before
 // it, S_in(p) = A(p-1) S_in(p-1) + B(p-1), a short walk that every thread of the second launch does for itself.
-constexpr int GRU_PIECE = 64;
+constexpr int GRU_PIECE = 32;
 
 __global__ void __launch_bounds__(128)
 min_gru_pieces_kernel(float* __restrict__ sumA, float* __restrict__ sumB, const float* __restrict__ pz,
@@ -83,7 +83,7 @@ min_gru_pieces_kernel(float* __restrict__ sumA, float* __restrict__ sumB, const 
   const size_t m0 = (size_t)seq_qstart[b] + t0;
   const float zb = bz ? bz[c] : 0.f, xb = bx ? bx[c] : 0.f;
   float A = 1.f, S = 0.f;
-#pragma unroll 4
+#pragma unroll 8
   for (int t = 0; t < rows; t++) {
     const float z = gs_sigmoid(pz[(m0 + t) * ldp + c] + zb);
     const float u = px[(m0 + t) * ldp + c] + xb;
@@ -118,7 +118,7 @@ min_gru_finish_kernel(TO* __restrict__ out, const float* __restrict__ sumA, floa
     const size_t at = ((size_t)b * max_pieces + q) * W + c;
     S = sumA[at] * S + sumB[at];
   }
-#pragma unroll 4
+#pragma unroll 8
   for (int t = 0; t < rows; t++) {
     const float z = gs_sigmoid(pz[(m0 + t) * ldp + c] + zb);
     const float u = px[(m0 + t) * ldp + c] + xb;
@@ -210,7 +210,7 @@ exp_gates_rows_kernel(float* __restrict__ decay, float* __restrict__ write, cons
 // come in side by side, the maximum walks the piece there (one thread a head, an addition and a maximum per row,
 // no trip to global memory inside the walk), and the exponentials are again formed side by side.
 constexpr int EXG_FLOATS = 3 * 4096;      // shared floats of a block: f, i and m of a piece
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __restrict__ mrow,
                  float* __restrict__ mstate, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                  const int* __restrict__ seq_qlen, int H, int piece) {
@@ -269,7 +269,9 @@ LEB_API int leb_exp_gates(float* decay, float* write, float* mrow, const float* 
   leb_launch(exp_gates_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, decay, write, pi, pf, ldp, bi, bf,
              cap, H, total);
   LEB_CHECK_LAUNCH("leb_exp_gates (rows)");
-  leb_launch(exp_gates_kernel, dim3(B), dim3(256), 0, st, decay, write, mrow, mstate, seq_slot, seq_qstart, seq_qlen, H, piece);
+  // many threads where a sequence brings many rows: the pieces' loads and exponentials are what takes the time
+  leb_launch(exp_gates_kernel, dim3(B), dim3(M > 4 * B ? 1024 : 128), 0, st, decay, write, mrow, mstate, seq_slot, seq_qstart,
+             seq_qlen, H, piece);
   LEB_CHECK_LAUNCH("leb_exp_gates");
   return 0;
 }
