@@ -479,9 +479,9 @@ def tevilix_config(width: int, ff: int, heads: int, kv_heads: int, dim: int, vdi
     model) alternate with the matrix memory with exponential gates; every layer has the dense feed-forward.  The
     attention takes the other design's head sizes and window, the matrix memory its recurrent layers' sizes."""
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
-           "rot": {"dims": dim, "base": 1000000.0, "scaling": {"factor": 2.0}}, "mask": {"size": window}}
-    par = {"left": att, "left_scale": 0.8, "right": {"width": width}, "right_scale": 1.1}
-    mem = {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim, "gate_cap": 12.0}
+           "rot": {"dims": dim, "base": 1000000.0, "scaling": {"factor": 4.0}}, "mask": {"size": window}}
+    par = {"left": att, "left_scale": 0.75, "right": {"width": width}, "right_scale": 1.25}
+    mem = {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim, "gate_cap": 10.0}
     ls = [{"type": "mlstm" if i % 2 else "parallel", "mixer": mem if i % 2 else par, "mlp": {"kind": "dense", "ff": ff}}
           for i in range(layers)]
     return {"architecture": "Tevilix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},

@@ -778,11 +778,11 @@ LEB_API int leb_attention_mixed(void* out, float* part, const void* q, int ldq, 
   const size_t esz = dtype == LEB_BF16 ? 2 : 4;
   // rows of a block: up to 128 (row, head) pairs, fewer when a sequence brings fewer rows; keys of a tile: 32, or
   // fewer where the tiles of all kv heads would not fit
-  const size_t budget = 200 * 1024;
+  const size_t room = 200 * 1024;
   int QT = max(1, min(max_qlen, min(16, 128 / H)));
   int KT = 32;
-  while (amx_smem(H, G, hd, vd, QT, KT, esz) > budget && QT > 1) QT = (QT + 1) / 2;
-  while (amx_smem(H, G, hd, vd, QT, KT, esz) > budget && KT > 8) KT /= 2;
+  while (amx_smem(H, G, hd, vd, QT, KT, esz) > room && QT > 1) QT = (QT + 1) / 2;
+  while (amx_smem(H, G, hd, vd, QT, KT, esz) > room && KT > 8) KT /= 2;
   const size_t smem = amx_smem(H, G, hd, vd, QT, KT, esz);
   LEB_REQUIRE(smem <= 227 * 1024, "leb_attention_mixed: %d kv heads of %d / %d do not fit shared memory", G, hd, vd);
   const int NP = QT * H;

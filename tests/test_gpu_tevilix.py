@@ -61,7 +61,7 @@ def test_attention_alone_whole_in_portions_and_batched(heads, kv, dim, vdim, sca
 
 
 MMA_CASES = [  # heads, kv heads, dim, vdim, window: sizes the tensor-core kernel takes
-    (4, 2, 128, 128, 72), (6, 2, 32, 16, 20), (32, 8, 64, 64, 200), (16, 4, 64, 32, 0), (3, 3, 64, 64, 70), (8, 1, 16, 8, 33),
+    (4, 2, 128, 64, 75), (6, 2, 32, 16, 20), (32, 8, 64, 64, 200), (16, 4, 64, 32, 0), (3, 3, 64, 64, 70), (8, 1, 16, 8, 33),
     (32, 2, 16, 64, 100), (2, 2, 256, 24, 150),
 ]
 
@@ -189,7 +189,7 @@ def test_a_key_just_inside_and_just_outside_the_window_in_prompts_and_in_decodin
 
 # ---- the minimal gated recurrent unit ---------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width", [48, 25, 320, 1])
+@pytest.mark.parametrize("width", [48, 25, 300, 1])
 def test_min_gru_alone_whole_in_portions_and_batched(width, dtype):
     D = 40
     rig = MixerRig("min_gru", dict(hidden_size=D, width=width), dtype, seed=9)
@@ -284,7 +284,7 @@ def test_mlstm_gates_reach_their_cap_and_the_running_maximum_is_carried():
 
 # ---- two mixers side by side -------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("a,b", [(0.8, 1.1), (1.0, 1.0), (0.0, 2.0)])
+@pytest.mark.parametrize("a,b", [(0.7, 1.3), (1.0, 1.0), (0.0, 2.0)])
 def test_mixers_side_by_side(a, b, dtype):
     from lastengine_b200.parts.base import PartSpec
     D = 40
@@ -341,7 +341,7 @@ MOE_CASES = [  # experts, top, groups, kept, scale, expert width
     (9, 2, 3, 2, 2.5, 14),
     (5, 5, 1, 1, 1.0, 8),          # every expert chosen
     (16, 4, 4, 1, 2.5, 24),
-    (16, 3, 2, 1, 2.5, 96),
+    (16, 3, 2, 1, 1.5, 80),
     (6, 3, None, None, 1.0, 24),   # no groups
 ]
 
@@ -547,13 +547,15 @@ def test_long_decoding_from_a_short_prompt(name, dtype, dirs):
     eng.cache.check()
 
 
-def plain_greedy(name, dirs, prompt, n):
+def plain_greedy(name, dirs, prompt, n, gap=2e-2):
+    """Greedy tokens of the plain implementation, and per token how far the choice is from falling the other way
+    (0 where a routing decision of the position is closer than `gap`)."""
     toks, out, margins = list(prompt), [], []
     for _ in range(n):
         lg, gaps = plain(name, dirs, toks)
         row = lg[-1]
         top = np.sort(row)[-2:]
-        margins.append(float((top[1] - top[0]) / np.abs(row).max()) if gaps[-1] > 2e-2 else 0.0)
+        margins.append(float((top[1] - top[0]) / np.abs(row).max()) if gaps[-1] > gap else 0.0)
         out.append(int(np.argmax(row)))
         toks.append(out[-1])
     return out, margins
@@ -569,7 +571,7 @@ def test_greedy_generation_through_the_entry_point(name, dtype, graphs, dirs):
     res = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=steps, stop_token_ids=[])
     compared = 0
     for p, got in zip(prompts, res.tokens):
-        want, margins = plain_greedy(name, dirs, p, steps)
+        want, margins = plain_greedy(name, dirs, p, steps, gap=1e-5 if dtype == "float32" else 2e-2)
         assert len(got) == steps
         for i in range(steps):
             if margins[i] < TOL[dtype]:

@@ -69,8 +69,8 @@ T_C = {
     "architecture": "Tevilix", "vocab": 97, "width": 40, "norm": {"eps": 1e-4},
     "layers": [
         layer("parallel", par(att(5, 5, 12, 20, 0.25, None, None, None, 1), 1.0, 25, 2.0), dense(56)),
-        layer("mlstm", mls(5, 10, 6, 12.0), None),
-        layer("parallel", par(att(2, 2, 24, 10, 0.4, 0, 10000.0, 2.0, 0), 0.6, 33, 1.1), moe(9, 2, 3, 2, 2.5, 14)),
+        layer("mlstm", mls(5, 10, 6, 9.0), None),
+        layer("parallel", par(att(2, 2, 24, 10, 0.4, 0, 10000.0, 2.0, 0), 0.6, 33, 1.1), moe(9, 2, 3, 2, 3.0, 14)),
         layer("mlstm", mls(1, 40, 40, 5.0), moe(5, 5, 1, 1, 1.0, 8)),
         layer("parallel", par(att(3, 1, 40, 24, 0.1, 40, 20000.0, 1.5, 64), 1.5, 16, 0.3), dense(24)),
     ],
@@ -80,11 +80,21 @@ T_C = {
 T_D = {
     "architecture": "Tevilix", "vocab": 320, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 9.5},
     "layers": [
-        layer("parallel", par(att(8, 4, 64, 32, 0.15, 32, 50000.0, 2.0, 128), 0.8, 200, 1.1), moe(16, 4, 4, 1, 2.5, 24)),
-        layer("mlstm", mls(3, 128, 64, 12.0), dense(80)),
+        layer("parallel", par(att(8, 4, 64, 32, 0.15, 32, 50000.0, 3.0, 128), 0.85, 200, 1.15), moe(16, 4, 4, 1, 1.75, 24)),
+        layer("mlstm", mls(3, 128, 64, 11.0), dense(80)),
         layer("mlstm", mls(6, 32, 16, 20.0), moe(10, 3, 5, 3, 1.0, 16)),
     ],
     "loop": {"start": 1, "stop": 2, "times": 3},
 }
 
-ALL = {"A": T_A, "B": T_B, "C": T_C, "D": T_D}
+# no size that is a multiple of 8 (not the width, no head size, no feed-forward width, not the vocabulary)
+T_E = {
+    "architecture": "Tevilix", "vocab": 101, "width": 42, "norm": {"eps": 1e-5}, "embedding": {"scale": 5.0},
+    "layers": [
+        layer("mlstm", mls(3, 14, 9, 7.0), moe(6, 2, 2, 1, 1.25, 10)),
+        layer("parallel", par(att(3, 1, 10, 6, 0.35, 6, 5000.0, 1.25, 17), 0.9, 27, 1.2), dense(30)),
+    ],
+    "loop": {"start": 1, "stop": 2, "times": 2},
+}
+
+ALL = {"A": T_A, "B": T_B, "C": T_C, "D": T_D, "E": T_E}
