@@ -88,6 +88,19 @@ __device__ __forceinline__ float gate_mul(float g, float u, int act) {
   }
   return silu_mul<T>(g, u);
 }
+// An activation without a gate in a storing epilogue (code 0) of the products that take it (the weight stream of a
+// decode step, dense and grouped): code LEB_PLAIN_ACT_BASE + a in the place of the gated activation, a as
+// leb_activation counts them (0 the erf form of gelu, 1 the square of relu, 2 the tanh form of gelu, 3 silu).  The
+// exact functions, as the activation kernel uses them: a row gives the same numbers through either.
+#define LEB_PLAIN_ACT_BASE 16
+#define LEB_PLAIN_ACT_OK(act, epi) ((act) >= LEB_PLAIN_ACT_BASE && (act) < LEB_PLAIN_ACT_BASE + 4 && (epi) == 0)
+__device__ __forceinline__ float plain_act(float z, int act) {
+  const int a = act - LEB_PLAIN_ACT_BASE;
+  if (a == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+  if (a == 1) { const float t = fmaxf(z, 0.f); return t * t; }
+  if (a == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
 // Device side.  pdl_trigger(): the next kernel on the stream may be scheduled (once every block
 // of this one has said so); it then runs its own start-up and waits in its pdl_wait() until this
 // kernel has completed.  Said first thing, even before this kernel's own wait: a product two

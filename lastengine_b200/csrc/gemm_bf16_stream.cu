@@ -277,6 +277,7 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
         v *= row_scale[col];
         if (in) {
           if (epilogue == 1) v += c_old[u];
+          else if (LEB_PLAIN_ACT_OK(act, epilogue)) v = plain_act(v, act);
           C[(size_t)col * ldc + n] = from_f32<TC>(v);
         }
         if (nm.emit_vals) {   // epilogue 1: the new residual, for the norm that follows
@@ -450,6 +451,7 @@ gemm_bf16_stream_grouped_kernel(TC* __restrict__ C, const bf16* __restrict__ A, 
         for (int w = 0; w < ST_WARPS; w++) v += red[w][rr / ST_ROWS][rr % ST_ROWS][col];
         TC* cp = C + (size_t)(ct.row0 + col) * ldc + n;
         if (epilogue == 1) v += to_f32(*cp);
+        else if (LEB_PLAIN_ACT_OK(act, epilogue)) v = plain_act(v, act);
         *cp = from_f32<TC>(v);
       }
     }
@@ -529,7 +531,8 @@ LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void
                                  void* emit_vals, const float* emit_g, float* emit_ssq, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_stream: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue) || LEB_PLAIN_ACT_OK(act_, epilogue),
+              "leb_gemm_bf16_stream: activation %d goes with neither the gated nor the storing epilogue", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream: %d rows; this kernel takes at most 16", M);
@@ -587,7 +590,8 @@ LEB_API int leb_gemm_bf16_stream_grouped(void* C, int c_dtype, const void* A, co
                                          size_t w_group_stride, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_stream_grouped: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue) || LEB_PLAIN_ACT_OK(act_, epilogue),
+              "leb_gemm_bf16_stream_grouped: activation %d goes with neither the gated nor the storing epilogue", act_);
   g_leb_gate_act = act_;
   if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
   LEB_REQUIRE(n_groups <= ST_MAX_GROUPS, "leb_gemm_bf16_stream_grouped: %d groups; at most %d", n_groups, ST_MAX_GROUPS);

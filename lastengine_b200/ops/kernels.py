@@ -563,6 +563,28 @@ GELU_ERF, RELU_SQUARED = 0, 1      # activations without a gate (leb_activation)
 PLAIN_ACTIVATIONS = {"gelu": 0, "relu_squared": 1, "gelu_tanh": 2, "silu": 3}
 
 
+PLAIN_ACT_BASE = 16      # a storing epilogue with an activation without a gate: STORE | (PLAIN_ACT_BASE + act) << 8
+
+
+def plain_act_epilogue(act: int) -> int:
+    """The epilogue code of a product that stores act(x . w^T); only for steps `stream_takes_plain_act` accepts."""
+    return (PLAIN_ACT_BASE + int(act)) << 8
+
+
+def stream_takes_plain_act(x: torch.Tensor, w: torch.Tensor, rows: int, n_groups: int = 0) -> bool:
+    """Whether `linear` would run these rows through the weight stream of a decode step (dense: up to SMALL_M
+    rows; grouped: up to 16 rows an expert), the products whose storing epilogue takes an activation without a
+    gate.  Every other product leaves float results for `activation`."""
+    if x.dtype != torch.bfloat16 or not w.is_contiguous():
+        return False
+    K = x.shape[1]
+    if K % 8 != 0 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0 or w.data_ptr() % 16 != 0:
+        return False
+    if n_groups:
+        return n_groups <= 256 and rows <= 16 * n_groups and (w.shape[1] * w.shape[2] * 2) % 16 == 0
+    return rows <= SMALL_M
+
+
 def activation(out: torch.Tensor, x: torch.Tensor, act: int) -> None:
     """out = act(x) in out's type; x float [M, F] (a column range is fine)."""
     _cuda(out, "activation.out")

@@ -93,8 +93,9 @@ class SwiGLU(FeedForward):
 @FEED_FORWARDS.register("dense")
 class DenseFeedForward(FeedForward):
     """f = W_down act(W_up h) without a gate; act is the erf form of gelu unless `activation` names another
-    ("relu_squared": max(z, 0)^2; "gelu_tanh"; "silu").  The up projection's float results go through the
-    activation in float.  `names`: (up, down)."""
+    ("relu_squared": max(z, 0)^2; "gelu_tanh"; "silu").  The up projection's float sums go through the
+    activation in float: in the product's epilogue in a decode step, in a launch of its own otherwise.
+    `names`: (up, down)."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu",
                  names: tuple[str, str] = ("up", "down")):
@@ -115,10 +116,14 @@ class DenseFeedForward(FeedForward):
     def forward(self, h, out, accumulate, batch, env) -> None:
         M = h.shape[0]
         ws = env.workspace
-        u = ws.get("ffn.u", (M, self.F), torch.float32)
-        kernels.linear(u, h, self.w1)
         a = ws.get("ffn.a", (M, self.F), env.dtype)
-        kernels.activation(a, u, self.act)
+        if kernels.stream_takes_plain_act(h, self.w1, M):
+            # a decode step: the weight stream applies the activation to its float sums before it stores
+            kernels.linear(a, h, self.w1, kernels.plain_act_epilogue(self.act))
+        else:
+            u = ws.get("ffn.u", (M, self.F), torch.float32)
+            kernels.linear(u, h, self.w1)
+            kernels.activation(a, u, self.act)
         kernels.linear(out, a, self.w2, kernels.ACCUMULATE if accumulate else kernels.STORE)
 
 
@@ -253,7 +258,9 @@ class SigmoidTopKMoE(FeedForward):
         xs = ws.get("moe.xs", (P, self.D), env.dtype)
         kernels.gather_rows(xs, h, sorted_pair, div=self.k)
         a = ws.get("moe.a", (P, self.Fe), env.dtype)
-        if not self.gated:
+        if not self.gated and kernels.stream_takes_plain_act(xs, self.w13, P, n_groups=self.E):
+            kernels.linear(a, xs, self.w13, kernels.plain_act_epilogue(self.act), group_offsets=offsets, rows_hint=P)
+        elif not self.gated:
             u = ws.get("moe.gu", (P, self.Fe), torch.float32)
             kernels.linear(u, xs, self.w13, group_offsets=offsets, rows_hint=P)
             kernels.activation(a, u, self.act)
