@@ -213,7 +213,8 @@ constexpr int EXG_FLOATS = 3 * 4096;      // shared floats of a block: f, i and 
 __global__ void __launch_bounds__(1024)
 exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __restrict__ mrow,
                  float* __restrict__ mstate, const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
-                 const int* __restrict__ seq_qlen, int H, int piece) {
+                 const int* __restrict__ seq_qlen, int H, int piece, const float* __restrict__ pi,
+                 const float* __restrict__ pf, int ldp, const float* __restrict__ bi, const float* __restrict__ bf, float cap) {
   __shared__ float sm[EXG_FLOATS];
   pdl_wait();
   const int b = blockIdx.x;
@@ -227,9 +228,17 @@ exp_gates_kernel(float* __restrict__ decay, float* __restrict__ write, float* __
   for (int t0 = 0; t0 < n; t0 += piece) {
     const int rows = min(piece, n - t0);
     for (int idx = threadIdx.x; idx < rows * H; idx += blockDim.x) {
-      const size_t at = (m0 + t0) * H + idx;
-      fs[idx] = decay[at];
-      is[idx] = write[at];
+      if (pi) {      // a step of few rows: the gates are formed here, in the one launch
+        const int t = idx / H, h = idx - t * H;
+        const float ri = pi[(m0 + t0 + t) * ldp + h] + (bi ? bi[h] : 0.f);
+        const float rf = pf[(m0 + t0 + t) * ldp + h] + (bf ? bf[h] : 0.f);
+        is[idx] = cap * tanhf(ri / cap);
+        fs[idx] = gs_log_sigmoid(cap * tanhf(rf / cap));
+      } else {
+        const size_t at = (m0 + t0) * H + idx;
+        fs[idx] = decay[at];
+        is[idx] = write[at];
+      }
     }
     __syncthreads();
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
@@ -265,13 +274,16 @@ LEB_API int leb_exp_gates(float* decay, float* write, float* mrow, const float* 
   LEB_REQUIRE(H <= 2048, "leb_exp_gates: %d heads (up to 2048)", H);
   LebPlainLaunches plain(true);
   const int piece = min(256, (EXG_FLOATS / 3 - H) / H);      // rows of a piece: f, i and m (one row more) fit
-  const size_t total = (size_t)M * H;
-  leb_launch(exp_gates_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, decay, write, pi, pf, ldp, bi, bf,
-             cap, H, total);
-  LEB_CHECK_LAUNCH("leb_exp_gates (rows)");
+  const bool few = M <= 4 * B;      // decode steps and the like: one launch forms the gates and walks them
+  if (!few) {
+    const size_t total = (size_t)M * H;
+    leb_launch(exp_gates_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, decay, write, pi, pf, ldp, bi,
+               bf, cap, H, total);
+    LEB_CHECK_LAUNCH("leb_exp_gates (rows)");
+  }
   // many threads where a sequence brings many rows: the pieces' loads and exponentials are what takes the time
-  leb_launch(exp_gates_kernel, dim3(B), dim3(M > 4 * B ? 1024 : 128), 0, st, decay, write, mrow, mstate, seq_slot, seq_qstart,
-             seq_qlen, H, piece);
+  leb_launch(exp_gates_kernel, dim3(B), dim3(few ? 128 : 1024), 0, st, decay, write, mrow, mstate, seq_slot, seq_qstart,
+             seq_qlen, H, piece, few ? pi : nullptr, pf, ldp, bi, bf, cap);
   LEB_CHECK_LAUNCH("leb_exp_gates");
   return 0;
 }

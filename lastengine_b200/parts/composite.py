@@ -4,7 +4,9 @@ The children are mixers of the registry, named by `PartSpec`; their tensors live
 of this part's prefix.  What they keep per sequence is kept together in one cache entry: at most one of them
 may hold keys and values, and their states must differ in shape (the cache files states by their shape).  A
 child whose output projection has an additive term (`output_bias()`) gets it added here, in float, before
-the weights a and b are applied.
+the weights a and b are applied.  Where both children form one product over their input rows with float results
+(`input_projection()`), the two products are one here: the matrices are stacked once at load (the children keep
+views of their rows), and each child's `forward` gets its columns of the result.
 """
 from __future__ import annotations
 
@@ -54,6 +56,13 @@ class ParallelMixers(Mixer):
                 if full in tensors:
                     own[rel] = tensors[full]
             part.load(own, env)
+        self.w_in, self.n_left = None, 0
+        wa = getattr(self.left, "input_projection", lambda: None)()
+        wb = getattr(self.right, "input_projection", lambda: None)()
+        if wa is not None and wb is not None and wa.dtype == wb.dtype and wa.shape[1] == wb.shape[1]:
+            self.w_in = torch.cat([wa, wb], dim=0).contiguous()
+            self.n_left = int(wa.shape[0])
+            self.left.w_in, self.right.w_in = self.w_in[: self.n_left], self.w_in[self.n_left:]      # views: one copy of the weights
 
     def cache_spec(self):
         flat = [s for side in self._specs for s in side]
@@ -88,11 +97,15 @@ class ParallelMixers(Mixer):
         y1 = ws.get("pair.left", (M, D), torch.float32)
         y2 = ws.get("pair.right", (M, D), torch.float32)
         bias = getattr(self.left, "output_bias", lambda: None)()
+        kl, kr = {}, {}
+        if self.w_in is not None:
+            proj = ws.get("pair.proj", (M, self.w_in.shape[0]), torch.float32)
+            kernels.linear(proj, h, self.w_in)
+            kl["proj"], kr["proj"] = proj[:, : self.n_left], proj[:, self.n_left:]
         if bias is not None:
-            self.left.forward(h, y1, False, batch, self._view(cache, 0), env, add_output_bias=False)
-        else:
-            self.left.forward(h, y1, False, batch, self._view(cache, 0), env)
-        self.right.forward(h, y2, False, batch, self._view(cache, 1), env)
+            kl["add_output_bias"] = False
+        self.left.forward(h, y1, False, batch, self._view(cache, 0), env, **kl)
+        self.right.forward(h, y2, False, batch, self._view(cache, 1), env, **kr)
         if getattr(self.right, "output_bias", lambda: None)() is not None:
             raise NotImplementedError("an output bias on the right-hand mixer")
         kernels.weighted_pair_sum(out, y1, self.a, y2, self.b, bias1=bias, accumulate=accumulate)

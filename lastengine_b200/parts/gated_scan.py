@@ -56,12 +56,17 @@ class MinGRUMixer(Mixer):
     def flops_per_row(self) -> int:
         return super().flops_per_row() + 8 * self.W
 
-    def forward(self, h, out, accumulate, batch, cache, env) -> None:
+    def input_projection(self):
+        """The matrix of this mixer's one product over its input rows (z | x | g); see `forward(proj=...)`."""
+        return self.w_in
+
+    def forward(self, h, out, accumulate, batch, cache, env, proj=None) -> None:
         W = self.W
         M = h.shape[0]
         ws = env.workspace
-        proj = ws.get("gru.proj", (M, 3 * W), torch.float32)
-        kernels.linear(proj, h, self.w_in)
+        if proj is None:
+            proj = ws.get("gru.proj", (M, 3 * W), torch.float32)
+            kernels.linear(proj, h, self.w_in)
         s = ws.get("gru.s", (M, W), env.dtype)
         n = kernels.min_gru_scratch(batch, W)
         scratch = ws.get("gru.pieces", (n,), torch.float32) if n else None

@@ -95,6 +95,11 @@ class MixedHeadsAttentionMixer(Mixer):
         if self.rot > self.hd:
             raise ValueError(f"{self.rot} rotated dimensions do not fit a head of {self.hd}")
 
+    def input_projection(self):
+        """The matrix of this mixer's one product over its input rows (q | k | v | gate), for whoever forms it
+        together with another mixer's; `forward(proj=...)` then takes the float results instead of forming them."""
+        return self.w_in
+
     def output_bias(self):
         """The additive term of the output projection, which whoever takes this mixer's float result adds."""
         return self.b_out
@@ -102,14 +107,15 @@ class MixedHeadsAttentionMixer(Mixer):
     def flops_per_query_key(self) -> int:
         return 2 * self.nh * (self.hd + self.vd + self.nh)
 
-    def forward(self, h, out, accumulate, batch, cache, env, add_output_bias: bool = True) -> None:
+    def forward(self, h, out, accumulate, batch, cache, env, add_output_bias: bool = True, proj=None) -> None:
         nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
         M = h.shape[0]
         ws = env.workspace
         if not cache.writable:
             raise NotImplementedError("this attention keeps its own keys and values")
-        proj = ws.get("mattn.proj", (M, self.w_in.shape[0]), torch.float32)
-        kernels.linear(proj, h, self.w_in)
+        if proj is None:
+            proj = ws.get("mattn.proj", (M, self.w_in.shape[0]), torch.float32)
+            kernels.linear(proj, h, self.w_in)
         n_qkv = (nh + nkv) * hd + nkv * vd
         q = ws.get("mattn.q", (M, nh * hd), env.dtype)
         kernels.pooled_attn_prep(q, cache.k, cache.v, proj[:, :n_qkv], self.b_in, self.q_norm_w, self.k_norm_w, self.eps,
