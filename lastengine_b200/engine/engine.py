@@ -323,10 +323,21 @@ class Engine:
         return self.weight_bytes() - sum(p.unread_weight_bytes(rows) for _, p in self.model.named_parts())
 
     def weight_bytes(self) -> int:
+        """Bytes of device memory the parts' tensors hold: every storage once (a part may keep views of a
+        matrix another part owns), parts inside parts included."""
+        from ..parts.base import Part
         seen, n = set(), 0
-        for _, part in self.model.named_parts():
+
+        def walk(part) -> None:
+            nonlocal n
             for v in vars(part).values():
-                if isinstance(v, torch.Tensor) and v.is_cuda and v.data_ptr() not in seen:
-                    seen.add(v.data_ptr())
-                    n += v.numel() * v.element_size()
+                if isinstance(v, torch.Tensor) and v.is_cuda:
+                    st = v.untyped_storage()
+                    if st.data_ptr() not in seen:
+                        seen.add(st.data_ptr())
+                        n += st.nbytes()
+                elif isinstance(v, Part):
+                    walk(v)
+        for _, part in self.model.named_parts():
+            walk(part)
         return n
