@@ -11,7 +11,7 @@ import torch
 import harness as H
 import plain_tevilix as P
 from harness import MixerRig, max_err as err, random_rows as inputs, whole_portions_and_batches
-from tevilix_configs import ALL, att, dense, mls, moe
+from tevilix_configs import ALL, att, dense, mls, moe, random_config
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -545,6 +545,31 @@ def test_long_decoding_from_a_short_prompt(name, dtype, dirs):
     got = H.run_tail(eng, r, tail=326)
     assert close(got, plain(name, dirs, r), dtype)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("seed", [201, 202, 203, 204, 205, 206, 207, 208])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Layer order, sizes, windows, loops and feed-forwards drawn at random: whole prompts, a tail token by token and an
+    unequal batch in 32-bit against the plain implementation, every position held; bfloat16 over the positions."""
+    from lastengine_b200 import Engine
+    from lastengine_b200.weights import write_model_dir
+    rng = np.random.default_rng(seed)
+    cfg = random_config(rng)
+    d = write_model_dir(cfg, str(tmp_path / "m"), seed=seed, norm_init="random")
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    reqs = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in (170, 40)]
+    want = [(P.forward(cfg, w, r), P.router_gaps(cfg, w, r)) for r in reqs]
+    eng = Engine.from_pretrained(d, dtype="float32", max_tokens=1024, max_seqs=4)
+    for r, wv in zip(reqs, want):
+        assert close(H.run_whole(eng, r), wv, "float32"), cfg
+    assert close(H.run_tail(eng, reqs[0], tail=70), want[0], "float32"), cfg
+    for g, wv in zip(H.run_batch(eng, reqs, [130, 9]), want):
+        assert close(g, wv, "float32"), cfg
+    eng.cache.check()
+    eng16 = Engine.from_pretrained(d, dtype="bfloat16", max_tokens=1024, max_seqs=4)
+    e = np.abs(H.run_whole(eng16, reqs[0]).double().numpy() - want[0][0]).max(-1) / np.abs(want[0][0]).max()
+    e = e[want[0][1] > 2e-2]
+    assert e.size == 0 or np.median(e) < H.TOL_BF16, cfg
 
 
 def plain_greedy(name, dirs, prompt, n, gap=2e-2):

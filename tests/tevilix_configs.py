@@ -98,3 +98,49 @@ T_E = {
 }
 
 ALL = {"A": T_A, "B": T_B, "C": T_C, "D": T_D, "E": T_E}
+
+
+def random_config(rng) -> dict:
+    """A configuration drawn at random: layer count and order, which layers have which feed-forward, every size (also
+    off the 8-number grid), windows around the page and tile borders or none, the rotated part, the looped range."""
+    def pick(xs):
+        return xs[int(rng.integers(0, len(xs)))]
+
+    def attention():
+        kv = pick([1, 1, 2, 2, 3, 4])
+        a = att(kv * pick([1, 2, 3, 4]), kv, pick([8, 16, 24, 32, 48, 64, 96, 128, 20, 36]), pick([8, 16, 32, 40, 64, 128, 12]),
+                float(rng.uniform(0.05, 0.4)), None, None, None, 0)
+        if rng.random() < 0.85:
+            a["rot"] = {"dims": pick([a["dim"], a["dim"] // 2, a["dim"] // 4]) // 2 * 2, "base": pick([100.0, 10000.0, 5e5])}
+            if rng.random() < 0.7:
+                a["rot"]["scaling"] = {"factor": pick([1.0, 2.0, 4.0, 1.5])}
+        if rng.random() < 0.85:
+            a["mask"] = {"size": pick([1, 2, 7, 31, 32, 33, 64, 65, 100, 128, 200])}
+        return a
+
+    def feed_forward():
+        r = rng.random()
+        if r < 0.2:
+            return None
+        if r < 0.5:
+            return dense(pick([24, 64, 100, 256]))
+        count, per = pick([1, 2, 3, 4]), pick([1, 2, 3, 4, 8])
+        keep = int(rng.integers(1, count + 1))
+        top = int(rng.integers(1, min(keep * per, 6) + 1))
+        return moe(count * per, top, count if rng.random() < 0.8 or keep < count else None, keep, pick([1.0, 2.0, 0.5]),
+                   pick([8, 24, 40, 96]))
+
+    layers = []
+    for _ in range(int(rng.integers(1, 5))):
+        if rng.random() < 0.5:
+            layers.append(layer("parallel", par(attention(), pick([1.0, 0.7, 1.3]), pick([16, 40, 100, 300, 33]),
+                                                pick([1.0, 1.2, 0.6])), feed_forward()))
+        else:
+            layers.append(layer("mlstm", mls(pick([1, 2, 3, 6]), pick([8, 16, 32, 64, 128, 20]), pick([8, 16, 64, 33, 128]),
+                                             pick([5.0, 10.0, 15.0, 30.0])), feed_forward()))
+    cfg = {"architecture": "Tevilix", "vocab": pick([64, 101, 500]), "width": pick([32, 40, 48, 64, 72, 96, 128, 192, 50, 84]),
+           "norm": {"eps": pick([1e-5, 1e-6])}, "embedding": {"scale": pick([1.0, 4.0, 9.0])}, "layers": layers}
+    if rng.random() < 0.6:
+        a = int(rng.integers(0, len(layers)))
+        cfg["loop"] = {"start": a, "stop": int(rng.integers(a, len(layers) + 1)), "times": int(rng.integers(1, 4))}
+    return cfg
